@@ -1,0 +1,361 @@
+"""Per-stage backward passes.
+
+* :func:`stage_backward` – full backward of one microbatch through one stage (reference pippy/_backward.py:9-102).
+* :func:`stage_backward_input` / :func:`stage_backward_weight` – the split used by zero-bubble schedules: the
+  input-gradient half runs on the critical path, the weight-gradient half is deferred
+  (upstream torch/distributed/pipelining/_backward.py:143-279 describes the same contract).  Two mechanisms are
+  combined: layers of this package (``ops.linear``) park their weight-gradient GEMMs in a
+  :class:`DeferredWeightGrads` queue while the input half runs, and anything else falls back to an
+  autograd-graph walk that stops at the parameters' producers.
+"""
+from __future__ import annotations
+
+import collections
+import threading
+from typing import Any, Callable, Dict, Iterable, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+from ._debug import map_debug_info
+
+
+def _flatten_outputs_and_grads(stage_output, output_grads) -> Tuple[List[torch.Tensor], List[Optional[torch.Tensor]]]:
+    outs: List[torch.Tensor] = []
+    grads: List[Optional[torch.Tensor]] = []
+
+    def visit(out, grad):
+        if isinstance(out, torch.Tensor):
+            if not out.requires_grad and out.grad_fn is None:
+                return
+            if grad is not None and not isinstance(grad, torch.Tensor):
+                raise TypeError(f"gradient for a tensor output must be a tensor or None, got {type(grad)}")
+            outs.append(out)
+            grads.append(grad)
+        elif isinstance(out, (tuple, list)):
+            if grad is None:
+                return
+            if not isinstance(grad, (tuple, list)) or len(grad) != len(out):
+                raise TypeError(f"output is a sequence of {len(out)} but its gradients are {type(grad)}")
+            for o, g in zip(out, grad):
+                visit(o, g)
+        elif isinstance(out, dict):
+            if grad is None:
+                return
+            if not isinstance(grad, dict) or set(grad.keys()) != set(out.keys()):
+                raise TypeError("output is a dict but its gradients do not have the same keys")
+            for k in out.keys():
+                visit(out[k], grad[k])
+        # anything else carries no gradient
+
+    visit(stage_output, output_grads)
+    return outs, grads
+
+
+def stage_backward(
+    stage_output,
+    output_grads,
+    input_values: Sequence[Any],
+    outputs_with_grads_idxs: Optional[List[int]] = None,
+) -> List[Optional[torch.Tensor]]:
+    """Backpropagates ``output_grads`` through the autograd graph of ``stage_output``.
+
+    Parameter gradients accumulate into ``.grad``; the return value lists the gradient of every entry of
+    ``input_values`` (``None`` for non-tensors and tensors without gradient).  For the last stage pass the loss
+    as ``stage_output`` and ``None`` as ``output_grads``.
+    """
+    if outputs_with_grads_idxs is not None:
+        stage_output = [stage_output[i] for i in outputs_with_grads_idxs]
+        output_grads = [output_grads[i] for i in outputs_with_grads_idxs]
+    try:
+        if output_grads is None and isinstance(stage_output, torch.Tensor):
+            outs, grads = [stage_output], [None]
+        elif output_grads is None and isinstance(stage_output, (tuple, list)):
+            outs = [o for o in stage_output if isinstance(o, torch.Tensor) and (o.requires_grad or o.grad_fn)]
+            grads = [None] * len(outs)
+        else:
+            outs, grads = _flatten_outputs_and_grads(stage_output, output_grads)
+        live = [(o, g) for o, g in zip(outs, grads) if not (g is None and o.numel() != 1)]
+        if live:
+            torch.autograd.backward([o for o, _ in live], grad_tensors=[g for _, g in live])
+        result: List[Optional[torch.Tensor]] = []
+        for v in input_values:
+            result.append(v.grad if isinstance(v, torch.Tensor) else None)
+        return result
+    except Exception as e:
+        raise RuntimeError(
+            f"""
+        Failed to run stage backward:
+        Stage output: {map_debug_info(stage_output)}
+        Output gradient: {map_debug_info(output_grads)}
+        Input: {map_debug_info(list(input_values))}
+        """
+        ) from e
+
+
+def _null_coalesce_accumulate(lhs, rhs):
+    """``lhs + rhs`` where either side may be ``None`` (reference _backward.py:107-117)."""
+    if lhs is None:
+        return rhs
+    if rhs is None:
+        return lhs
+    return torch.add(lhs, rhs)
+
+
+# --------------------------------------------------------------------------------------------
+# Deferred weight gradients (the fast path for this package's own layers)
+# --------------------------------------------------------------------------------------------
+class DeferredWeightGrads:
+    """FIFO of weight-gradient closures recorded while an input-gradient pass runs.
+
+    A layer's autograd backward asks :func:`current_deferral` for the active queue; when there is one it
+    computes only the input gradient and calls :meth:`defer` with a closure that, when run later, accumulates the
+    weight gradient.
+    """
+
+    def __init__(self) -> None:
+        self._items: List[Callable[[], None]] = []
+
+    def defer(self, fn: Callable[[], None]) -> None:
+        self._items.append(fn)
+
+    def __len__(self) -> int:
+        return len(self._items)
+
+    def run(self) -> None:
+        items, self._items = self._items, []
+        for fn in items:
+            fn()
+
+
+_tls = threading.local()
+
+
+def current_deferral() -> Optional[DeferredWeightGrads]:
+    return getattr(_tls, "queue", None)
+
+
+class defer_weight_grads:
+    """Context manager: weight-gradient work of this package's layers goes to ``queue`` instead of running."""
+
+    def __init__(self, queue: Optional[DeferredWeightGrads]):
+        self.queue = queue
+
+    def __enter__(self):
+        self.prev = getattr(_tls, "queue", None)
+        _tls.queue = self.queue
+        return self.queue
+
+    def __exit__(self, *exc):
+        _tls.queue = self.prev
+        return False
+
+
+# --------------------------------------------------------------------------------------------
+# Generic split for arbitrary modules: walk the autograd graph
+# --------------------------------------------------------------------------------------------
+def _grad_fn_of(t: torch.Tensor):
+    if t.grad_fn is not None:
+        return t.grad_fn
+    if t.requires_grad:
+        return torch.autograd.graph.get_gradient_edge(t).node  # AccumulateGrad of a leaf
+    return None
+
+
+def _reachable_from(roots: Iterable[Any]) -> set:
+    seen = set()
+    stack = [r for r in roots if r is not None]
+    while stack:
+        node = stack.pop()
+        if node in seen:
+            continue
+        seen.add(node)
+        for nxt, _ in node.next_functions:
+            if nxt is not None and nxt not in seen:
+                stack.append(nxt)
+    return seen
+
+
+class _WeightGradPlan:
+    """What :func:`stage_backward_input` leaves behind for :func:`stage_backward_weight`."""
+
+    def __init__(self) -> None:
+        self.deferred: Optional[DeferredWeightGrads] = None
+        # (boundary node, captured grads per input slot, params whose accumulators hang below it)
+        self.boundaries: List[Tuple[Any, Tuple[Optional[torch.Tensor], ...], List[torch.nn.Parameter]]] = []
+        self.full_backward: Optional[Tuple[List[torch.Tensor], List[Optional[torch.Tensor]]]] = None
+
+
+def stage_backward_input(
+    stage_outputs_or_loss: Sequence[torch.Tensor],
+    output_grads: Optional[Sequence[Optional[torch.Tensor]]],
+    input_values: Sequence[torch.Tensor],
+    weights: Iterator[torch.nn.Parameter],
+) -> Tuple[List[Optional[torch.Tensor]], _WeightGradPlan]:
+    """Computes only the gradients of ``input_values``; parameter gradients are postponed.
+
+    Returns ``(input_grads, plan)``; hand ``plan`` to :func:`stage_backward_weight` to finish. When no input
+    requires a gradient (the first stage) nothing is computed now and the plan holds a full backward.
+    """
+    outs = [o for o in stage_outputs_or_loss if isinstance(o, torch.Tensor) and (o.requires_grad or o.grad_fn)]
+    if output_grads is None:
+        grads: List[Optional[torch.Tensor]] = [None] * len(outs)
+    else:
+        pairs = [
+            (o, g)
+            for o, g in zip(stage_outputs_or_loss, output_grads)
+            if isinstance(o, torch.Tensor) and (o.requires_grad or o.grad_fn) and g is not None
+        ]
+        outs = [o for o, _ in pairs]
+        grads = [g for _, g in pairs]
+    grads = [g if g is not None else torch.ones_like(o) for o, g in zip(outs, grads)]
+
+    plan = _WeightGradPlan()
+    diff_inputs = [v for v in input_values if isinstance(v, torch.Tensor) and v.requires_grad]
+    weights = [w for w in weights if w.requires_grad]
+    if not diff_inputs:
+        plan.full_backward = (outs, grads)
+        return [None] * len(input_values), plan
+    if not outs:
+        return [None] * len(input_values), plan
+
+    # Nodes on a path output -> input.  A node *off* that path whose parent is *on* it is a boundary: its
+    # gradient is what the weight half needs.  Hooks capture those gradients during the input pass.
+    input_nodes = {_grad_fn_of(v) for v in diff_inputs}
+    weight_nodes = {}
+    for w in weights:
+        node = _grad_fn_of(w)
+        if node is not None:
+            weight_nodes.setdefault(node, []).append(w)
+
+    # reverse reachability: which nodes can reach an input leaf
+    out_roots = [o.grad_fn for o in outs if o.grad_fn is not None]
+    order: List[Any] = []
+    seen = set()
+    stack = [(r, False) for r in out_roots]
+    while stack:
+        node, done = stack.pop()
+        if done:
+            order.append(node)
+            continue
+        if node in seen:
+            continue
+        seen.add(node)
+        stack.append((node, True))
+        for nxt, _ in node.next_functions:
+            if nxt is not None and nxt not in seen:
+                stack.append((nxt, False))
+    reaches_input = set()
+    for node in order:  # children before parents
+        if node in input_nodes or any(n is not None and n in reaches_input for n, _ in node.next_functions):
+            reaches_input.add(node)
+
+    # boundary edges: parent on the input path, child not on it but leading to some weight
+    leads_to_weight_cache: Dict[Any, List[torch.nn.Parameter]] = {}
+
+    def weights_below(node) -> List[torch.nn.Parameter]:
+        hit = leads_to_weight_cache.get(node)
+        if hit is not None:
+            return hit
+        found: List[torch.nn.Parameter] = []
+        for n in _reachable_from([node]):
+            found.extend(weight_nodes.get(n, ()))
+        leads_to_weight_cache[node] = found
+        return found
+
+    captured: Dict[Any, Dict[int, torch.Tensor]] = collections.defaultdict(dict)
+    handles = []
+    boundary_edges: List[Tuple[Any, int]] = []
+    seen_edges = set()
+    for node in order:
+        if node not in reaches_input:
+            continue
+        for child, slot in node.next_functions:
+            if child is None or child in reaches_input or (child, slot) in seen_edges:
+                continue
+            if not weights_below(child):
+                continue
+            seen_edges.add((child, slot))
+            boundary_edges.append((child, slot))
+    # output nodes that do not reach any input at all are boundaries themselves (pure weight branches)
+    for o, g in zip(outs, grads):
+        node = o.grad_fn
+        if node is not None and node not in reaches_input and weights_below(node):
+            edge = torch.autograd.graph.get_gradient_edge(o)
+            key = (edge.node, edge.output_nr)
+            if key not in seen_edges:
+                seen_edges.add(key)
+                boundary_edges.append(key)
+                captured[key[0]][key[1]] = g
+
+    from .backward import defer_weight_grads as _ctx  # noqa: F401  (self import keeps name local for clarity)
+
+    queue = DeferredWeightGrads()
+    plan.deferred = queue
+
+    # capture the gradient flowing into each boundary edge via tensor-free pre-hooks
+    def make_hook(node):
+        def hook(grad_outputs):
+            for slot, g in enumerate(grad_outputs):
+                if g is not None and (node, slot) in seen_edges:
+                    prev = captured[node].get(slot)
+                    captured[node][slot] = g if prev is None else prev + g
+            return None
+
+        return hook
+
+    hooked = set()
+    for node, _slot in boundary_edges:
+        if node not in hooked and hasattr(node, "register_prehook"):
+            handles.append(node.register_prehook(make_hook(node)))
+            hooked.add(node)
+
+    try:
+        with defer_weight_grads(queue):
+            in_grads = torch.autograd.grad(outs, diff_inputs, grad_outputs=grads, retain_graph=True, allow_unused=True)
+    finally:
+        for h in handles:
+            h.remove()
+
+    for node, slot in boundary_edges:
+        g = captured.get(node, {}).get(slot)
+        if g is None:
+            continue
+        plan.boundaries.append((torch.autograd.graph.GradientEdge(node, slot), (g,), weights_below(node)))
+
+    result: List[Optional[torch.Tensor]] = []
+    it = iter(in_grads)
+    for v in input_values:
+        if isinstance(v, torch.Tensor) and v.requires_grad:
+            g = next(it)
+            result.append(g)
+        else:
+            result.append(None)
+    return result, plan
+
+
+def stage_backward_weight(weights: Iterator[torch.nn.Parameter], plan: _WeightGradPlan, retain_graph: bool = False) -> None:
+    """Finishes what :func:`stage_backward_input` postponed: accumulates parameter gradients into ``.grad``."""
+    if plan.full_backward is not None:
+        outs, grads = plan.full_backward
+        if outs:
+            torch.autograd.backward(outs, grad_tensors=grads, retain_graph=retain_graph)
+        plan.full_backward = None
+        return
+    if plan.deferred is not None:
+        plan.deferred.run()
+    if plan.boundaries:
+        # group by parameter set so each autograd.grad call touches its own subgraph once
+        for edge, grads, params in plan.boundaries:
+            params = [p for p in params if p.requires_grad]
+            if not params:
+                continue
+            with defer_weight_grads(None):
+                dws = torch.autograd.grad((edge,), params, grad_outputs=grads, retain_graph=True, allow_unused=True)
+            for p, dw in zip(params, dws):
+                if dw is None:
+                    continue
+                if p.grad is None:
+                    p.grad = dw.detach()
+                else:
+                    p.grad = p.grad + dw
+        plan.boundaries = []
