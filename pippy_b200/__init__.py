@@ -1,0 +1,20 @@
+"""pippy_b200: pipeline parallelism for PyTorch on Blackwell (sm_100a)."""
+from ._debug import logger  # noqa: F401
+from .backward import stage_backward, stage_backward_input, stage_backward_weight  # noqa: F401
+from .manual_stage import ManualPipelineStage, get_stage_shapes, validate_stage_shapes  # noqa: F401
+from .microbatch import (  # noqa: F401
+    TensorChunkSpec,
+    merge_chunks,
+    split_args_kwargs_into_chunks,
+    sum_reducer,
+)
+from .schedules import (  # noqa: F401
+    Schedule1F1B,
+    ScheduleGPipe,
+    ScheduleInterleaved1F1B,
+    ScheduleInterleavedZeroBubble,
+    ScheduleLoopedBFS,
+    ScheduleZeroBubble,
+)
+
+__version__ = "0.1.0"

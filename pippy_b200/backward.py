@@ -180,8 +180,8 @@ class _WeightGradPlan:
 
     def __init__(self) -> None:
         self.deferred: Optional[DeferredWeightGrads] = None
-        # (boundary node, captured grads per input slot, params whose accumulators hang below it)
-        self.boundaries: List[Tuple[Any, Tuple[Optional[torch.Tensor], ...], List[torch.nn.Parameter]]] = []
+        # (gradient edges of a split node, the gradients captured there, parameters below its off-path children)
+        self.boundaries: List[Tuple[Tuple[Any, ...], Tuple[torch.Tensor, ...], List[torch.nn.Parameter]]] = []
         self.full_backward: Optional[Tuple[List[torch.Tensor], List[Optional[torch.Tensor]]]] = None
 
 
@@ -249,66 +249,74 @@ def stage_backward_input(
         if node in input_nodes or any(n is not None and n in reaches_input for n, _ in node.next_functions):
             reaches_input.add(node)
 
-    # boundary edges: parent on the input path, child not on it but leading to some weight
-    leads_to_weight_cache: Dict[Any, List[torch.nn.Parameter]] = {}
+    # Split points: nodes ON the input path with at least one child OFF it that leads to parameters.  The gradient
+    # arriving at such a node is captured during the input pass; the weight pass restarts autograd from the node
+    # with that gradient and asks only for the parameters hanging below its off-path children.
+    below_cache: Dict[Any, List[torch.nn.Parameter]] = {}
 
     def weights_below(node) -> List[torch.nn.Parameter]:
-        hit = leads_to_weight_cache.get(node)
+        hit = below_cache.get(node)
         if hit is not None:
             return hit
         found: List[torch.nn.Parameter] = []
         for n in _reachable_from([node]):
             found.extend(weight_nodes.get(n, ()))
-        leads_to_weight_cache[node] = found
+        below_cache[node] = found
         return found
 
-    captured: Dict[Any, Dict[int, torch.Tensor]] = collections.defaultdict(dict)
-    handles = []
-    boundary_edges: List[Tuple[Any, int]] = []
-    seen_edges = set()
+    split_nodes: List[Tuple[Any, List[torch.nn.Parameter]]] = []
+    claimed: Dict[int, int] = {}
+    conflict = False
     for node in order:
         if node not in reaches_input:
             continue
-        for child, slot in node.next_functions:
-            if child is None or child in reaches_input or (child, slot) in seen_edges:
+        off_params: List[torch.nn.Parameter] = []
+        for child, _slot in node.next_functions:
+            if child is None or child in reaches_input:
                 continue
-            if not weights_below(child):
-                continue
-            seen_edges.add((child, slot))
-            boundary_edges.append((child, slot))
-    # output nodes that do not reach any input at all are boundaries themselves (pure weight branches)
+            off_params.extend(weights_below(child))
+        if not off_params:
+            continue
+        uniq = list({id(p): p for p in off_params}.values())
+        for p_ in uniq:
+            claimed[id(p_)] = claimed.get(id(p_), 0) + 1
+            if claimed[id(p_)] > 1:
+                conflict = True  # a parameter reachable from two split points would be counted twice
+        split_nodes.append((node, uniq))
+    # outputs whose whole history is off the input path contribute only to parameters
+    weight_only_outputs = []
     for o, g in zip(outs, grads):
         node = o.grad_fn
         if node is not None and node not in reaches_input and weights_below(node):
-            edge = torch.autograd.graph.get_gradient_edge(o)
-            key = (edge.node, edge.output_nr)
-            if key not in seen_edges:
-                seen_edges.add(key)
-                boundary_edges.append(key)
-                captured[key[0]][key[1]] = g
+            weight_only_outputs.append((o, g))
+            for p_ in weights_below(node):
+                claimed[id(p_)] = claimed.get(id(p_), 0) + 1
+                if claimed[id(p_)] > 1:
+                    conflict = True
 
-    from .backward import defer_weight_grads as _ctx  # noqa: F401  (self import keeps name local for clarity)
+    if conflict:
+        # exact split is not possible with this graph shape: run the whole backward now, nothing is deferred
+        torch.autograd.backward(outs, grad_tensors=grads)
+        return [v.grad if isinstance(v, torch.Tensor) else None for v in input_values], plan
 
     queue = DeferredWeightGrads()
     plan.deferred = queue
+    captured: Dict[Any, Tuple[Optional[torch.Tensor], ...]] = {}
+    handles = []
 
-    # capture the gradient flowing into each boundary edge via tensor-free pre-hooks
     def make_hook(node):
         def hook(grad_outputs):
-            for slot, g in enumerate(grad_outputs):
-                if g is not None and (node, slot) in seen_edges:
-                    prev = captured[node].get(slot)
-                    captured[node][slot] = g if prev is None else prev + g
+            prev = captured.get(node)
+            if prev is None:
+                captured[node] = tuple(grad_outputs)
+            else:
+                captured[node] = tuple(_null_coalesce_accumulate(a, b) for a, b in zip(prev, grad_outputs))
             return None
 
         return hook
 
-    hooked = set()
-    for node, _slot in boundary_edges:
-        if node not in hooked and hasattr(node, "register_prehook"):
-            handles.append(node.register_prehook(make_hook(node)))
-            hooked.add(node)
-
+    for node, _params in split_nodes:
+        handles.append(node.register_prehook(make_hook(node)))
     try:
         with defer_weight_grads(queue):
             in_grads = torch.autograd.grad(outs, diff_inputs, grad_outputs=grads, retain_graph=True, allow_unused=True)
@@ -316,11 +324,21 @@ def stage_backward_input(
         for h in handles:
             h.remove()
 
-    for node, slot in boundary_edges:
-        g = captured.get(node, {}).get(slot)
-        if g is None:
+    for node, params in split_nodes:
+        got = captured.get(node)
+        if got is None:
             continue
-        plan.boundaries.append((torch.autograd.graph.GradientEdge(node, slot), (g,), weights_below(node)))
+        edges = []
+        edge_grads = []
+        for slot, g in enumerate(got):
+            if g is not None:
+                edges.append(torch.autograd.graph.GradientEdge(node, slot))
+                edge_grads.append(g)
+        if edges:
+            plan.boundaries.append((tuple(edges), tuple(edge_grads), params))
+    for o, g in weight_only_outputs:
+        edge = torch.autograd.graph.get_gradient_edge(o)
+        plan.boundaries.append(((edge,), (g,), weights_below(o.grad_fn)))
 
     result: List[Optional[torch.Tensor]] = []
     it = iter(in_grads)
@@ -345,12 +363,12 @@ def stage_backward_weight(weights: Iterator[torch.nn.Parameter], plan: _WeightGr
         plan.deferred.run()
     if plan.boundaries:
         # group by parameter set so each autograd.grad call touches its own subgraph once
-        for edge, grads, params in plan.boundaries:
+        for edges, grads, params in plan.boundaries:
             params = [p for p in params if p.requires_grad]
             if not params:
                 continue
             with defer_weight_grads(None):
-                dws = torch.autograd.grad((edge,), params, grad_outputs=grads, retain_graph=True, allow_unused=True)
+                dws = torch.autograd.grad(edges, params, grad_outputs=grads, retain_graph=True, allow_unused=True)
             for p, dw in zip(params, dws):
                 if dw is None:
                     continue

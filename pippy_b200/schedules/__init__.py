@@ -1,0 +1,16 @@
+from .actions import Action, Op, Schedule, add_send_recv, dump_csv, format_schedule, load_csv, validate
+from .generators import gpipe, interleaved_1f1b, looped_bfs, one_f_one_b, with_reduce_grad, zero_bubble
+from .runtime import (
+    PipelineSchedule,
+    PipelineScheduleMulti,
+    PipelineScheduleSingle,
+    Schedule1F1B,
+    ScheduleGPipe,
+    ScheduleInterleaved1F1B,
+    ScheduleInterleavedZeroBubble,
+    ScheduleLoopedBFS,
+    ScheduleTimeout,
+    ScheduleZeroBubble,
+    sorted_batch_isend_irecv,
+)
+from .simulator import SimResult, ideal_bubble, simulate

@@ -1,0 +1,217 @@
+"""Pure generators of per-rank compute orders for every supported schedule.
+
+Stage ``s`` of an interleaved (multi-stage-per-rank) pipeline lives on rank ``s % P`` (reference
+pippy/_PipelineStage.py:129-136), so a rank's local stages are ``rank + k*P``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+from .actions import Action, Op, Schedule
+
+
+def gpipe(P: int, n_mb: int, backward: bool = True) -> Schedule:
+    """Fill-drain: all forwards, then all backwards in microbatch order (reference PipelineSchedule.py:279-355)."""
+    out: Schedule = {}
+    for r in range(P):
+        acts = [Action(r, Op.F, m) for m in range(n_mb)]
+        if backward:
+            acts += [Action(r, Op.B, m) for m in range(n_mb)]
+        out[r] = acts
+    return out
+
+
+def one_f_one_b(P: int, n_mb: int, backward: bool = True, reference_warmup: bool = False) -> Schedule:
+    """1F1B. ``reference_warmup`` uses the reference's 2*(P-r-1) warm-up forwards
+    (PipelineSchedule.py:379-387) instead of the textbook P-r-1; the bubble is the same, the reference form keeps
+    twice as many activations in flight."""
+    out: Schedule = {}
+    for r in range(P):
+        if not backward:
+            out[r] = [Action(r, Op.F, m) for m in range(n_mb)]
+            continue
+        depth = (P - r - 1) * (2 if reference_warmup else 1)
+        warm = min(n_mb, depth)
+        acts: List[Action] = []
+        f = b = 0
+        for _ in range(warm):
+            acts.append(Action(r, Op.F, f))
+            f += 1
+        while f < n_mb:
+            acts.append(Action(r, Op.F, f))
+            f += 1
+            acts.append(Action(r, Op.B, b))
+            b += 1
+        while b < n_mb:
+            acts.append(Action(r, Op.B, b))
+            b += 1
+        out[r] = acts
+    return out
+
+
+def looped_bfs(P: int, v: int, n_mb: int, backward: bool = True) -> Schedule:
+    """Breadth-first over a rank's local stages: every microbatch through local stage 0, then stage 1, ...;
+    backward in reverse stage order (reference PipelineSchedule.py:517-569)."""
+    out: Schedule = {}
+    for r in range(P):
+        stages = [r + k * P for k in range(v)]
+        acts = [Action(s, Op.F, m) for s in stages for m in range(n_mb)]
+        if backward:
+            acts += [Action(s, Op.B, m) for s in reversed(stages) for m in range(n_mb)]
+        out[r] = acts
+    return out
+
+
+def _interleaved_orders(P: int, v: int, n_mb: int, r: int):
+    """Forward and backward visiting orders of rank r: microbatches advance in rounds of P per local stage."""
+    total = v * n_mb
+    f_count = [0] * v
+    b_count = [0] * v
+    f_seq, b_seq = [], []
+    for step in range(total):
+        k = (step // P) % v
+        f_seq.append((r + k * P, f_count[k]))
+        f_count[k] += 1
+        kb = v - 1 - ((step // P) % v)
+        b_seq.append((r + kb * P, b_count[kb]))
+        b_count[kb] += 1
+    return f_seq, b_seq
+
+
+def interleaved_1f1b(P: int, v: int, n_mb: int, backward: bool = True) -> Schedule:
+    """Interleaved 1F1B with ``v`` stages per rank (reference PipelineSchedule.py:572-778, warm-up math :623-640)."""
+    if n_mb % P != 0:
+        raise ValueError(
+            f"Interleaved 1F1B requires the number of microbatches ({n_mb}) to be a multiple of the pipeline "
+            f"group size ({P})"
+        )
+    out: Schedule = {}
+    total = v * n_mb
+    for r in range(P):
+        f_seq, b_seq = _interleaved_orders(P, v, n_mb, r)
+        if not backward:
+            out[r] = [Action(s, Op.F, m) for s, m in f_seq]
+            continue
+        warm = min((v - 1) * P + 2 * ((P - 1) - r), total)
+        acts: List[Action] = [Action(s, Op.F, m) for s, m in f_seq[:warm]]
+        b = 0
+        for i in range(warm, total):
+            s, m = f_seq[i]
+            acts.append(Action(s, Op.F, m))
+            s, m = b_seq[b]
+            acts.append(Action(s, Op.B, m))
+            b += 1
+        while b < total:
+            s, m = b_seq[b]
+            acts.append(Action(s, Op.B, m))
+            b += 1
+        out[r] = acts
+    return out
+
+
+def zero_bubble(
+    P: int,
+    v: int,
+    n_mb: int,
+    max_pending_w: Optional[int] = None,
+    extra_in_flight: int = 0,
+    cost_f: int = 1,
+    cost_i: int = 1,
+    cost_w: int = 1,
+) -> Schedule:
+    """Zero-bubble schedule with the backward split into I (input grads) and W (weight grads).
+
+    Built by list scheduling on a unit-cost timeline: each rank visits forwards and input-gradient passes in the
+    interleaved-1F1B orders, always prefers a ready I, then a ready F while fewer than
+    ``(v-1)*P + (P-1-r) + 1 + extra_in_flight`` microbatch-stages are in flight, and fills every remaining gap
+    with the oldest deferred W (``max_pending_w`` bounds how many weight-gradient passes may be parked, and with
+    them the activations they keep alive).  With v == 1 this is the ZB-H1 shape; v > 1 corresponds to
+    upstream's interleaved zero-bubble schedule.
+    """
+    if v > 1 and n_mb % P != 0:
+        raise ValueError(
+            f"interleaved zero-bubble requires the number of microbatches ({n_mb}) to be a multiple of the "
+            f"pipeline group size ({P})"
+        )
+    S = P * v
+    total = v * n_mb
+    if max_pending_w is None:
+        max_pending_w = max(2 * P, 4)
+    f_seq, i_seq = {}, {}
+    for r in range(P):
+        f_seq[r], i_seq[r] = _interleaved_orders(P, v, n_mb, r)
+    cap = {r: (v - 1) * P + (P - 1 - r) + 1 + extra_in_flight for r in range(P)}
+    fp = {r: 0 for r in range(P)}
+    ip = {r: 0 for r in range(P)}
+    wq: Dict[int, List] = {r: [] for r in range(P)}
+    in_flight = {r: 0 for r in range(P)}
+    busy_until = {r: 0 for r in range(P)}
+    finish: Dict[tuple, int] = {}  # (stage, kind, mb) -> completion time
+    out: Schedule = {r: [] for r in range(P)}
+    t = 0
+    remaining = P * total * 3
+    guard = 0
+    while remaining > 0:
+        guard += 1
+        if guard > 100 * P * total + 1000:
+            raise RuntimeError("zero-bubble list scheduling failed to converge")
+        for r in range(P):
+            if busy_until[r] > t:
+                continue
+            choice = None
+            if ip[r] < total:
+                s, m = i_seq[r][ip[r]]
+                dep_ok = finish.get((s, "F", m), 1 << 60) <= t and (
+                    s == S - 1 or finish.get((s + 1, "I", m), 1 << 60) <= t
+                )
+                if dep_ok:
+                    choice = ("I", s, m)
+            if choice is None and len(wq[r]) > max_pending_w:
+                choice = ("W",) + wq[r][0]
+            if choice is None and fp[r] < total and in_flight[r] < cap[r]:
+                s, m = f_seq[r][fp[r]]
+                if s == 0 or finish.get((s - 1, "F", m), 1 << 60) <= t:
+                    choice = ("F", s, m)
+            if choice is None and wq[r]:
+                choice = ("W",) + wq[r][0]
+            if choice is None:
+                continue
+            kind, s, m = choice
+            if kind == "F":
+                fp[r] += 1
+                in_flight[r] += 1
+                dur = cost_f
+                out[r].append(Action(s, Op.F, m))
+            elif kind == "I":
+                ip[r] += 1
+                in_flight[r] -= 1
+                wq[r].append((s, m))
+                dur = cost_i
+                out[r].append(Action(s, Op.I, m))
+            else:
+                wq[r].pop(0)
+                dur = cost_w
+                out[r].append(Action(s, Op.W, m))
+            finish[(s, kind, m)] = t + dur
+            busy_until[r] = t + dur
+            remaining -= 1
+        t += 1
+    return out
+
+
+def with_reduce_grad(schedule: Schedule) -> Schedule:
+    """Appends a REDUCE_GRAD action right after the last weight-producing action (B or W) of every stage."""
+    out: Schedule = {}
+    for r, acts in schedule.items():
+        last: Dict[int, int] = {}
+        for idx, a in enumerate(acts):
+            if a.op in (Op.B, Op.W):
+                last[a.stage] = idx
+        new: List[Action] = []
+        for idx, a in enumerate(acts):
+            new.append(a)
+            for s, li in last.items():
+                if li == idx:
+                    new.append(Action(s, Op.REDUCE_GRAD))
+        out[r] = new
+    return out
