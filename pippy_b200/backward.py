@@ -211,7 +211,8 @@ def stage_backward_input(
 
     plan = _WeightGradPlan()
     diff_inputs = [v for v in input_values if isinstance(v, torch.Tensor) and v.requires_grad]
-    weights = [w for w in weights if w.requires_grad]
+    # parameters whose owning op writes their gradient itself (ops.functional) never go through the graph walk
+    weights = [w for w in weights if w.requires_grad and not getattr(w, "_pb_direct_grad", False)]
     if not diff_inputs:
         plan.full_backward = (outs, grads)
         return [None] * len(input_values), plan

@@ -1,0 +1,276 @@
+// RMSNorm and LayerNorm, forward and backward, bf16 activations with fp32 statistics.
+//
+// Forward: one CTA per group of rows, each row held in registers (16-byte loads), one pass.
+// Backward: a persistent grid walks the rows; every thread keeps its slice of the weight (and bias)
+// gradient in registers and writes one partial row per CTA to a scratch buffer [grid, H] which a
+// second kernel folds.  dx is produced in the same pass.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+extern "C" void pb_count_launch(int n);
+
+namespace pbn {
+
+constexpr int THREADS = 256;
+constexpr int MAX_VEC = 4;  // up to 4 x 8 bf16 per thread -> H <= 8192
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < THREADS / 32) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// kLayer = false: RMSNorm (y = x * rstd * w);  true: LayerNorm (y = (x - mean) * rstd * w + b)
+template <bool kLayer, int NV>
+__global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           const __nv_bfloat16* __restrict__ b,
+                                                           __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                                                           float* __restrict__ rstd_out, int T, int H, float eps) {
+  __shared__ float red[THREADS / 32];
+  const int nvec = H / 8;  // 16-byte vectors per row
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    float v[NV][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = threadIdx.x + i * THREADS;
+      if (c < nvec) {
+        unpack8(xr[c], v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s += v[i][j];
+          ss += v[i][j] * v[i][j];
+        }
+      }
+    }
+    float mean = 0.f;
+    if (kLayer) {
+      mean = block_sum(s, red) / H;
+      // second moment around the mean, from registers
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        if (c < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float d = v[i][j] - mean;
+            sq += d * d;
+          }
+        }
+      }
+      ss = sq;
+    }
+    const float var = block_sum(ss, red) / H;
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      rstd_out[row] = rstd;
+      if (kLayer) mean_out[row] = mean;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = threadIdx.x + i * THREADS;
+      if (c < nvec) {
+        float wv[8], o[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(w) + c), wv);
+        if (kLayer) {
+          float bv[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(b) + c), bv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * wv[j] + bv[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
+        }
+        yr[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// dx and per-CTA partial dw (and db). partial: [gridDim.x, 2, H] fp32 (db half unused for RMSNorm).
+template <bool kLayer, int NV>
+__global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                           const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           const float* __restrict__ mean_in,
+                                                           const float* __restrict__ rstd_in,
+                                                           __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
+                                                           int T, int H) {
+  __shared__ float red[THREADS / 32];
+  const int nvec = H / 8;
+  float dw_acc[NV][8], db_acc[NV][8], wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dw_acc[i][j] = 0.f;
+      db_acc[i][j] = 0.f;
+      wv[i][j] = 0.f;
+    }
+    if (c < nvec) unpack8(__ldg(reinterpret_cast<const uint4*>(w) + c), wv[i]);
+  }
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    const float rstd = rstd_in[row];
+    const float mean = kLayer ? mean_in[row] : 0.f;
+    float xh[NV][8], g[NV][8];
+    float s1 = 0.f, s2 = 0.f;  // sum(g*w*xhat), sum(g*w)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = threadIdx.x + i * THREADS;
+      if (c < nvec) {
+        unpack8(xr[c], xh[i]);
+        unpack8(gr[c], g[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          const float gw = g[i][j] * wv[i][j];
+          s1 += gw * xh[i][j];
+          s2 += gw;
+          dw_acc[i][j] += g[i][j] * xh[i][j];
+          if (kLayer) db_acc[i][j] += g[i][j];
+        }
+      }
+    }
+    const float m1 = block_sum(s1, red) / H;
+    const float m2 = kLayer ? block_sum(s2, red) / H : 0.f;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = threadIdx.x + i * THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] * wv[i][j] - m2 - xh[i][j] * m1);
+        dxr[c] = pack8(o);
+      }
+    }
+  }
+  float* pw = partial + (size_t)blockIdx.x * 2 * H;
+  float* pb = pw + H;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * THREADS;
+    if (c < nvec) {
+      float4* d0 = reinterpret_cast<float4*>(pw + c * 8);
+      d0[0] = make_float4(dw_acc[i][0], dw_acc[i][1], dw_acc[i][2], dw_acc[i][3]);
+      d0[1] = make_float4(dw_acc[i][4], dw_acc[i][5], dw_acc[i][6], dw_acc[i][7]);
+      if (kLayer) {
+        float4* d1 = reinterpret_cast<float4*>(pb + c * 8);
+        d1[0] = make_float4(db_acc[i][0], db_acc[i][1], db_acc[i][2], db_acc[i][3]);
+        d1[1] = make_float4(db_acc[i][4], db_acc[i][5], db_acc[i][6], db_acc[i][7]);
+      }
+    }
+  }
+}
+
+// out[h] (+)= sum_p partial[p, which, h]; writes fp32 (accumulate) or bf16.
+__global__ void norm_reduce_partials(const float* __restrict__ partial, int parts, int H, int which, float* out_f32,
+                                     __nv_bfloat16* out_bf16, int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[((size_t)p * 2 + which) * H + h];
+  if (out_f32) out_f32[h] = accumulate ? out_f32[h] + s : s;
+  else out_bf16[h] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[h]) + s : s);
+}
+
+}  // namespace pbn
+
+extern "C" {
+
+// Number of scratch floats pb_norm_bwd needs for hidden size H.
+long long pb_norm_bwd_scratch_floats(int H, int sm_count) { return (long long)sm_count * 2 * 2 * H; }
+
+int pb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T, int H,
+                float eps, int layer_norm, void* stream_) {
+  using namespace pbn;
+  if (H % 8 != 0 || H > THREADS * MAX_VEC * 8) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = T < 148 * 8 ? T : 148 * 8;
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto B = reinterpret_cast<const __nv_bfloat16*>(b);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  const int nv = (H / 8 + THREADS - 1) / THREADS;
+#define PB_FWD(L, NVV) norm_fwd_kernel<L, NVV><<<grid, THREADS, 0, stream>>>(X, W, B, Y, mean, rstd, T, H, eps)
+  if (layer_norm) {
+    if (nv <= 1) PB_FWD(true, 1); else if (nv <= 2) PB_FWD(true, 2); else PB_FWD(true, 4);
+  } else {
+    if (nv <= 1) PB_FWD(false, 1); else if (nv <= 2) PB_FWD(false, 2); else PB_FWD(false, 4);
+  }
+#undef PB_FWD
+  pb_count_launch(1);
+  return (int)cudaGetLastError();
+}
+
+// dw_f32/db_f32 (fp32, accumulate) or dw_bf16/db_bf16; scratch: pb_norm_bwd_scratch_floats(H, sm_count) floats.
+int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                float* dw_f32, float* db_f32, void* dw_bf16, void* db_bf16, int accumulate, float* scratch, int T, int H,
+                int layer_norm, int sm_count, void* stream_) {
+  using namespace pbn;
+  if (H % 8 != 0 || H > THREADS * MAX_VEC * 8) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int grid = sm_count * 2;
+  if (grid > T) grid = T;
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  const int nv = (H / 8 + THREADS - 1) / THREADS;
+#define PB_BWD(L, NVV) norm_bwd_kernel<L, NVV><<<grid, THREADS, 0, stream>>>(DY, X, W, mean, rstd, DX, scratch, T, H)
+  if (layer_norm) {
+    if (nv <= 1) PB_BWD(true, 1); else if (nv <= 2) PB_BWD(true, 2); else PB_BWD(true, 4);
+  } else {
+    if (nv <= 1) PB_BWD(false, 1); else if (nv <= 2) PB_BWD(false, 2); else PB_BWD(false, 4);
+  }
+#undef PB_BWD
+  const int rb = (H + 255) / 256;
+  norm_reduce_partials<<<rb, 256, 0, stream>>>(scratch, grid, H, 0, dw_f32, reinterpret_cast<__nv_bfloat16*>(dw_bf16),
+                                               accumulate);
+  int launches = 2;
+  if (layer_norm) {
+    norm_reduce_partials<<<rb, 256, 0, stream>>>(scratch, grid, H, 1, db_f32,
+                                                 reinterpret_cast<__nv_bfloat16*>(db_bf16), accumulate);
+    launches = 3;
+  }
+  pb_count_launch(launches);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,238 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 statement of the same op (needs a B200)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+@pytest.fixture(autouse=True)
+def _seed_and_check():
+    torch.manual_seed(0)
+    yield
+    from pippy_b200.ops import _lib
+
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+def test_gemm_layouts(variant, a_mn, b_mn):
+    from pippy_b200.ops.gemm import gemm
+
+    M, N, K = 1000, 776, 520
+    a = _bf16(K, M) if a_mn else _bf16(M, K)
+    b = _bf16(K, N) if b_mn else _bf16(N, K)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    out = gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), variant=variant)
+    assert _rel(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+def test_gemm_epilogues(variant):
+    from pippy_b200.ops.gemm import gemm
+
+    M, N, K = 512, 768, 256
+    a, b = _bf16(M, K), _bf16(N, K)
+    bias, res = _bf16(N), _bf16(M, N)
+    r0 = a.float() @ b.float().t()
+    assert _rel(gemm(a, b, bias=bias, residual=res, variant=variant), r0 + bias.float() + res.float()) < 1e-2
+    aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b, bias=bias, act=1, aux=aux, variant=variant)
+    assert _rel(out, F.gelu(r0 + bias.float(), approximate="tanh")) < 1e-2
+    assert _rel(aux, r0 + bias.float()) < 1e-2
+    acc = torch.ones(M, N, device="cuda")
+    gemm(a, b, out=acc, accumulate=True, variant=variant)
+    assert _rel(acc, r0 + 1) < 1e-4
+
+
+@pytest.mark.parametrize("H", [768, 4096, 5120])
+@pytest.mark.parametrize("layer", [False, True])
+def test_norm(H, layer):
+    from pippy_b200.ops import functional as pf
+
+    T = 515
+    x = _bf16(T, H).requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_()
+    b = (0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_() if layer else None
+    dy = _bf16(T, H)
+    y = pf.layer_norm(x, w, b, 1e-5) if layer else pf.rms_norm(x, w, 1e-5)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    if layer:
+        bf = b.detach().float().requires_grad_()
+        yr = F.layer_norm(xf, (H,), wf, bf, 1e-5)
+    else:
+        yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xf.grad) < 1e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
+    if layer:
+        assert _rel(b.grad, bf.grad) < 2e-2
+
+
+def test_swiglu_and_gelu_linear():
+    from pippy_b200.ops import functional as pf
+
+    T, Fd = 300, 1408
+    gu = _bf16(T, 2 * Fd).requires_grad_()
+    d = _bf16(T, Fd)
+    out = pf.swiglu(gu)
+    out.backward(d)
+    gf = gu.detach().float().requires_grad_()
+    g, u = gf.chunk(2, -1)
+    ref = F.silu(g) * u
+    ref.backward(d.float())
+    assert _rel(out, ref) < 1e-2 and _rel(gu.grad, gf.grad) < 1e-2
+
+    x = _bf16(T, 256).requires_grad_()
+    w = _bf16(512, 256, scale=0.05).requires_grad_()
+    bias = _bf16(512, scale=0.1).requires_grad_()
+    res = _bf16(T, 512).requires_grad_()
+    dy = _bf16(T, 512)
+    y = pf.linear(x, w, bias, residual=res, activation="gelu_tanh")
+    y.backward(dy)
+    xf, wf, bf, rf = (t.detach().float().requires_grad_() for t in (x, w, bias, res))
+    yr = F.gelu(F.linear(xf, wf, bf), approximate="tanh") + rf
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xf.grad) < 2e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
+    assert _rel(bias.grad, bf.grad) < 2e-2
+    assert _rel(res.grad, rf.grad) < 1e-2
+
+
+def test_linear_main_grad_accumulates_fp32():
+    from pippy_b200.ops import functional as pf
+
+    x = _bf16(256, 128).requires_grad_()
+    w = _bf16(384, 128, scale=0.05).requires_grad_()
+    w.main_grad = torch.zeros(384, 128, device="cuda")
+    for _ in range(2):
+        pf.linear(x, w).backward(torch.ones(256, 384, device="cuda", dtype=torch.bfloat16))
+    ref = 2 * torch.ones(256, 384, device="cuda").t() @ x.detach().float()
+    assert w.grad is None and _rel(w.main_grad, ref) < 1e-3
+
+
+def test_cross_entropy():
+    from pippy_b200.ops import functional as pf
+
+    T, V, Vp = 257, 1000, 1024
+    logits = _bf16(T, Vp, scale=2.0).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    tgt[5] = -100
+    loss = pf.cross_entropy(logits, tgt, vocab_size=V, reduction="mean")
+    (loss * 3.0).backward()
+    lf = logits.detach().float().requires_grad_()
+    ref = F.cross_entropy(lf[:, :V], tgt, reduction="mean", ignore_index=-100)
+    (ref * 3.0).backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * abs(ref.item())
+    assert (logits.grad.float() - lf.grad).abs().max().item() < 2e-4
+    assert logits.grad[:, V:].abs().max().item() == 0
+
+
+def test_embedding():
+    from pippy_b200.ops import functional as pf
+
+    V, H, B, S = 500, 256, 3, 64
+    wte = _bf16(V, H).requires_grad_()
+    wpe = _bf16(S, H).requires_grad_()
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    out = pf.embedding(ids, wte, wpe, S)
+    d = _bf16(B * S, H)
+    out.backward(d)
+    wf, pf_ = wte.detach().float().requires_grad_(), wpe.detach().float().requires_grad_()
+    pos = torch.arange(B * S, device="cuda") % S
+    ref = F.embedding(ids.reshape(-1), wf) + F.embedding(pos, pf_)
+    ref.backward(d.float())
+    assert _rel(out, ref) < 1e-2
+    assert _rel(wte.grad, wf.grad) < 1e-2 and _rel(wpe.grad, pf_.grad) < 1e-2
+
+
+def test_fused_adamw_matches_torch():
+    import torch.nn as nn
+
+    from pippy_b200.optim import FlatParams, FusedAdamW
+
+    ps = [nn.Parameter(_bf16(300, 70)), nn.Parameter(_bf16(129))]
+    ref = [nn.Parameter(p.detach().float().clone()) for p in ps]
+    flat = FlatParams(ps)
+    opt = FusedAdamW(flat, lr=1e-2, weight_decay=0.1, master_weights=True)
+    ropt = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.1)
+    for _ in range(3):
+        for p, r in zip(ps, ref):
+            g = torch.randn_like(r)
+            p.main_grad.copy_(g)
+            r.grad = g.clone()
+        opt.step(zero_grad=True)
+        ropt.step()
+    for p, r in zip(ps, ref):
+        assert _rel(p, r) < 1e-2
+        assert p.main_grad.abs().max().item() == 0
+    assert _rel(opt.master[0][: ps[0].numel()].view_as(ref[0]), ref[0]) < 1e-5
+
+
+def _attn_ref(q, k, v, causal, scale):
+    # q [B,S,Hq,D], k/v [B,S,Hkv,D] fp32
+    rep = q.shape[2] // k.shape[2]
+    k = k.repeat_interleave(rep, dim=2)
+    v = v.repeat_interleave(rep, dim=2)
+    att = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
+    if causal:
+        S = q.shape[1]
+        att = att.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    return torch.einsum("bhqk,bkhd->bqhd", att.softmax(-1), v)
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D", [(2, 256, 4, 4, 128), (1, 384, 8, 2, 128), (2, 320, 4, 4, 64), (1, 1024, 2, 1, 64)])
+def test_flash_attention_fwd_bwd(B, S, Hq, Hkv, D):
+    from pippy_b200.ops import functional as pf
+
+    T = B * S
+    qkv = _bf16(T, (Hq + 2 * Hkv) * D).requires_grad_()
+    do = _bf16(T, Hq * D)
+    out = pf.rope_attention(qkv, None, None, B, S, Hq, Hkv, D)
+    out.backward(do)
+    qf = qkv.detach().float().requires_grad_()
+    q = qf[:, : Hq * D].view(B, S, Hq, D)
+    k = qf[:, Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = qf[:, (Hq + Hkv) * D :].view(B, S, Hkv, D)
+    ref = _attn_ref(q, k, v, True, 1 / math.sqrt(D)).reshape(T, Hq * D)
+    ref.backward(do.float())
+    assert _rel(out, ref) < 2e-2
+    g, gr = qkv.grad.float(), qf.grad
+    for name, sl in (("dq", slice(0, Hq * D)), ("dk", slice(Hq * D, (Hq + Hkv) * D)), ("dv", slice((Hq + Hkv) * D, None))):
+        assert _rel(g[:, sl], gr[:, sl]) < 3e-2, name
+
+
+def test_rope_attention_with_rotary():
+    from pippy_b200.ops import functional as pf
+
+    B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+    T = B * S
+    base = _bf16(T, (Hq + 2 * Hkv) * D)
+    cos, sin = pf.rope_tables(S, D, 10000.0, "cuda")
+    qkv = base.clone().requires_grad_()
+    do = _bf16(T, Hq * D)
+    qkv_in = qkv * 1  # the op rotates its input in place; give it a private buffer
+    out = pf.rope_attention(qkv_in, cos, sin, B, S, Hq, Hkv, D)
+    out.backward(do)
+    qf = base.float().requires_grad_()
+    q = pf._rope_ref(qf[:, : Hq * D].view(B, S, Hq, D), cos, sin)
+    k = pf._rope_ref(qf[:, Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D), cos, sin)
+    v = qf[:, (Hq + Hkv) * D :].view(B, S, Hkv, D)
+    ref = _attn_ref(q.float(), k.float(), v, True, 1 / math.sqrt(D)).reshape(T, Hq * D)
+    ref.backward(do.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(qkv.grad, qf.grad) < 3e-2
