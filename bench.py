@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput (tokens/s) of a Llama-2-7B-shaped decoder under pipeline parallelism.
+
+Config (the one the baseline names): 32 layers, d_model 4096, 32 heads, SwiGLU 11008, vocab 32000, bf16,
+global batch 64 x seq 4096, 32 microbatches, 2 virtual stages per rank, AdamW lr 3e-4, PP = number of GPUs.
+Strong scaling: the global batch is fixed, so per-GPU work shrinks as GPUs are added.
+
+  python bench.py --gpus 1 --steps 2 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+      bench.py --gpus 8 --steps 2 --warmup 3
+  python bench.py --impl reference ...     # the unmodified reference (baseline/_ref) on the same config
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with inputs resident on the
+device; ``e2e`` repeats the measurement through the public API with a pinned-host -> device copy of every step's
+inputs and a device -> host read of the loss inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_PUBLISHED = None  # the reference publishes no throughput number
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--schedule", default=None, help="interleaved_1f1b | zero_bubble | 1f1b | gpipe | looped_bfs")
+    ap.add_argument("--model", default="llama2-7b", help="llama2-7b | llama-small (for quick checks only)")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--microbatches", type=int, default=32)
+    ap.add_argument("--virtual", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--timing", action="store_true", help="also report the measured bubble of the last step")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, power = [], [], []
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                    power.append(float(parts[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load": drop idle samples taken before the first kernel or after the last
+        busy = [c for c, p in zip(sm, power) if p > 300] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+def model_config(name: str):
+    from pippy_b200.models.llama import LlamaConfig
+
+    if name == "llama2-7b":
+        return LlamaConfig.llama2_7b(), "Llama-2-7B shape (32L, d4096, 32h, ffn 11008, vocab 32000)"
+    if name == "llama-small":
+        return LlamaConfig(vocab_size=32000, dim=2048, n_layers=8, n_heads=16, ffn_dim=5504), "llama-small (8L, d2048)"
+    raise SystemExit(f"unknown model {name}")
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import ref_bench  # noqa: E402
+
+        ref_bench.main(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from pippy_b200.ops import _lib
+    from pippy_b200.train import build_llama_pipeline
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg, model_desc = model_config(args.model)
+    schedule = args.schedule or ("interleaved_1f1b" if world == 1 else "zero_bubble")
+    virtual = args.virtual
+    if schedule in ("gpipe", "1f1b"):
+        virtual = 1
+    pipe = build_llama_pipeline(
+        cfg, args.batch, args.seq, args.microbatches, device, schedule=schedule, virtual_stages=virtual,
+        lr=3e-4, weight_decay=0.1, record_timing=args.timing,
+    )
+
+    # synthetic data of the named shape: uniform token ids, labels = ids shifted by one
+    g = torch.Generator().manual_seed(1234)
+    n_sets = 2
+    host_ids = [torch.randint(0, cfg.vocab_size, (args.batch, args.seq), generator=g).pin_memory() for _ in range(n_sets)]
+    host_lbl = []
+    for ids in host_ids:
+        lbl = torch.roll(ids, -1, dims=1)
+        lbl[:, -1] = -100
+        host_lbl.append(lbl.pin_memory())
+    dev_ids = [t.to(device) for t in host_ids] if pipe.holds_first else [None] * n_sets
+    dev_lbl = [t.to(device) for t in host_lbl] if pipe.holds_last else [None] * n_sets
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- warm-up
+    loss = None
+    for i in range(args.warmup):
+        loss = pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
+    barrier()
+    _lib.check_device_errors()
+
+    # ---------------------------------------------------------------- device-timed region
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        loss = pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
+    ev1.record()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    launches = sum_over_ranks(float(_lib.launch_count() - launches0))
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_device_errors()
+    final_loss = float(loss.item()) if loss is not None else None
+    bubble = None
+    if args.timing and pipe.schedule.last_step_stats is not None:
+        bubble = max_over_ranks(pipe.schedule.last_step_stats["bubble"])
+
+    # ---------------------------------------------------------------- end-to-end region (H2D inputs + D2H loss each step)
+    e2e = None
+    if not args.no_e2e:
+        h2d = d2h = 0
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            ids = lbl = None
+            if pipe.holds_first:
+                ids = host_ids[i % n_sets].to(device, non_blocking=True)
+                h2d += ids.numel() * ids.element_size()
+            if pipe.holds_last:
+                lbl = host_lbl[i % n_sets].to(device, non_blocking=True)
+                h2d += lbl.numel() * lbl.element_size()
+            l = pipe.train_step(ids, lbl)
+            if l is not None:
+                host_loss = l.float().cpu()  # device -> host read of the step's result
+                d2h += host_loss.numel() * host_loss.element_size()
+        e1.record()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+        tokens = args.batch * args.seq * args.steps
+        e2e = {
+            "value": tokens / (e2e_ms * 1e-3),
+            "unit": "tokens/s",
+            "h2d_bytes_per_step": int(sum_over_ranks(float(h2d)) / args.steps),
+            "d2h_bytes_per_step": int(sum_over_ranks(float(d2h)) / args.steps),
+            "ms_per_step": e2e_ms / args.steps,
+        }
+        _lib.check_device_errors()
+
+    if rank == 0:
+        tokens = args.batch * args.seq * args.steps
+        value = tokens / (ms_total * 1e-3)
+        ms_per_step = ms_total / args.steps
+        tflops = cfg.flops_per_token(args.seq) * value / 1e12
+        out = {
+            "metric": "tokens/sec (whole job, device-timed, max over ranks)",
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None if BASELINE_PUBLISHED is None else value / BASELINE_PUBLISHED,
+            "dtype": "bf16",
+            "data": "synthetic (uniform token ids, labels shifted by one; random-init weights)",
+            "impl": "ours",
+            "config": {
+                "model": model_desc,
+                "global_batch": args.batch,
+                "seq_len": args.seq,
+                "microbatches": args.microbatches,
+                "parallelism": f"pp{world}" + (f"x{virtual}v" if virtual > 1 else ""),
+                "schedule": schedule,
+                "optimizer": "AdamW lr 3e-4 (fused, fp32 moments, fp32 gradient accumulation)",
+                "l2": "inputs larger than L2 (13.5 GB of weights and GBs of activations stream every step)",
+            },
+            "model_tflops_per_gpu": tflops / world,
+            "final_loss": final_loss,
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": int(launches),
+        }
+        if bubble is not None:
+            out["bubble_measured"] = bubble
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -53,6 +53,14 @@ class FlatParams:
         for p in self.params:
             p.grad = None
 
+    def fold_autograd_grads(self) -> None:
+        """Adds gradients that autograd left in ``param.grad`` (ops outside this package, or the CPU path) into
+        the flat buffer and clears them, so the flat buffer is the single source of truth."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None
+
     def buckets(self, bucket_numel: int) -> List[slice]:
         """Contiguous slices of the flat buffers, cut at parameter boundaries, in reverse parameter order
         (gradients of late layers are complete first during backward)."""
@@ -93,6 +101,7 @@ class FusedAdamW:
         self.step_count += 1
         b1, b2 = self.betas
         for g, m, v, master in zip(self.groups, self.m, self.v, self.master):
+            g.fold_autograd_grads()
             if g.data.is_cuda and g.data.dtype == torch.bfloat16 and g.grad.dtype == torch.float32:
                 rc = _lib.lib().pb_adamw(
                     _lib.ptr(g.data), _lib.ptr(master), _lib.ptr(g.grad), _lib.ptr(m), _lib.ptr(v),

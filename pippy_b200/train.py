@@ -1,0 +1,118 @@
+"""Convenience builders that assemble stages, schedule and optimizer for the model families of this package.
+
+These are thin: everything they do can be done by hand with ``ManualPipelineStage`` (or ``pipeline()`` +
+``PipelineStage``), a ``Schedule*`` class and ``FusedAdamW``; the benchmark and the examples use them so that they
+exercise exactly the public API a user would.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .manual_stage import ManualPipelineStage
+from .models.llama import LlamaConfig, build_llama_stage, causal_lm_loss
+from .optim import FlatParams, FusedAdamW
+from .schedules import (
+    Schedule1F1B,
+    ScheduleGPipe,
+    ScheduleInterleaved1F1B,
+    ScheduleInterleavedZeroBubble,
+    ScheduleLoopedBFS,
+)
+
+SCHEDULES = {
+    "gpipe": ScheduleGPipe,
+    "1f1b": Schedule1F1B,
+    "looped_bfs": ScheduleLoopedBFS,
+    "interleaved_1f1b": ScheduleInterleaved1F1B,
+    "zero_bubble": ScheduleInterleavedZeroBubble,
+}
+
+
+@dataclass
+class Pipeline:
+    stages: List[ManualPipelineStage]
+    schedule: Any
+    optimizer: Optional[FusedAdamW]
+    flat: Optional[FlatParams]
+    n_microbatches: int
+    holds_first: bool
+    holds_last: bool
+    losses: List[torch.Tensor] = field(default_factory=list)
+
+    def train_step(self, inputs=None, target=None) -> Optional[torch.Tensor]:
+        """One optimizer step over one global batch. The rank holding the first stage passes ``inputs``, the rank
+        holding the last stage passes ``target`` and gets the mean loss (a device scalar) back."""
+        self.losses.clear()
+        args = (inputs,) if self.holds_first and inputs is not None else ()
+        if self.holds_last:
+            self.schedule.step(*args, target=target, losses=self.losses)
+        else:
+            self.schedule.step(*args)
+        if self.optimizer is not None:
+            self.optimizer.step(grad_scale=1.0 / self.n_microbatches, zero_grad=True)
+        if self.holds_last and self.losses:
+            return torch.stack([l.detach() for l in self.losses]).mean()
+        return None
+
+
+def build_llama_pipeline(
+    cfg: LlamaConfig,
+    global_batch: int,
+    seq_len: int,
+    n_microbatches: int,
+    device: torch.device,
+    schedule: str = "interleaved_1f1b",
+    virtual_stages: int = 1,
+    group: Optional[dist.ProcessGroup] = None,
+    dtype: torch.dtype = torch.bfloat16,
+    lr: float = 3e-4,
+    weight_decay: float = 0.1,
+    master_weights: bool = False,
+    with_optimizer: bool = True,
+    grad_reducer: Any = None,
+    seed: int = 0,
+    record_timing: bool = False,
+    schedule_kwargs: Optional[dict] = None,
+) -> Pipeline:
+    """Builds this rank's Llama stages (stage ``rank + k * pp_size`` for k < virtual_stages), the schedule and
+    the fused optimizer."""
+    if dist.is_initialized():
+        pp_rank, pp_size = dist.get_rank(group), dist.get_world_size(group)
+    else:
+        pp_rank, pp_size = 0, 1
+    num_stages = pp_size * virtual_stages
+    if global_batch % n_microbatches != 0:
+        raise ValueError(f"global batch {global_batch} is not divisible into {n_microbatches} microbatches")
+    mb = global_batch // n_microbatches
+    stages: List[ManualPipelineStage] = []
+    params = []
+    for k in range(virtual_stages):
+        s = pp_rank + k * pp_size
+        torch.manual_seed(seed + s)
+        module = build_llama_stage(cfg, s, num_stages, device=device, dtype=dtype)
+        inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        stages.append(ManualPipelineStage(module, s, num_stages, device, n_microbatches, input_args=inp,
+                                          output_args=out, group=group))
+        params.extend(module.parameters())
+    flat = opt = None
+    if with_optimizer:
+        flat = FlatParams(params)
+        opt = FusedAdamW(flat, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
+    cls = SCHEDULES[schedule]
+    kw = dict(schedule_kwargs or {})
+    kw.update(loss_fn=causal_lm_loss, grad_reducer=grad_reducer, record_timing=record_timing)
+    if schedule in ("gpipe", "1f1b"):
+        if virtual_stages != 1:
+            raise ValueError(f"schedule {schedule!r} runs one stage per rank")
+        sched = cls(stages[0], n_microbatches, **kw)
+    else:
+        sched = cls(stages, n_microbatches, **kw)
+    return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
+                    holds_last=((num_stages - 1) % pp_size == pp_rank))
