@@ -291,6 +291,9 @@ class PipelineStageBase:
         composite.extend(root)  # extra positional args pass through (first stage called with more args)
         return composite
 
+    def _compose_inputs_for_forward(self, mb: int, args: Tuple[Any, ...]) -> List[Any]:
+        return self._compose_inputs(mb, args)
+
     def forward_maybe_with_nosync(self, *args, **kwargs):
         from torch.nn.parallel import DistributedDataParallel
 
@@ -307,7 +310,7 @@ class PipelineStageBase:
                 f"[{self.stage_index}] microbatch {mb} has no receive info; did the schedule prepare "
                 f"{self.chunks} microbatches?"
             )
-        composite_args = self._compose_inputs(mb, tuple(args))
+        composite_args = self._compose_inputs_for_forward(mb, tuple(args))
         try:
             output = self.forward_maybe_with_nosync(*composite_args, **kwargs)
         except Exception as e:

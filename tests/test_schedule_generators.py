@@ -1,0 +1,124 @@
+"""Properties of the schedule generators, checked on CPU with the simulator."""
+import os
+
+import pytest
+
+from pippy_b200.schedules import actions as A
+from pippy_b200.schedules import generators as G
+from pippy_b200.schedules import simulator as S
+from pippy_b200.schedules.actions import Action, Op
+
+
+def _check(schedule, P, v, n):
+    s2r = lambda s: s % P
+    A.validate(schedule, P * v, n, s2r)
+    full = A.add_send_recv(schedule, s2r, P * v)
+    for r, acts in full.items():
+        sends = [a for a in acts if a.op in (Op.SEND_F, Op.SEND_B)]
+        recvs = [a for a in acts if a.op in (Op.RECV_F, Op.RECV_B)]
+        assert len(sends) == len(recvs) or P > 1
+    cost = {Op.F: 1.0 / v, Op.B: 2.0 / v, Op.I: 1.0 / v, Op.W: 1.0 / v}
+    return S.simulate(full, s2r, P * v, cost)
+
+
+@pytest.mark.parametrize("P,n", [(2, 4), (4, 8), (4, 3), (8, 32)])
+def test_gpipe_and_1f1b_have_the_analytic_bubble(P, n):
+    for sched in (G.gpipe(P, n), G.one_f_one_b(P, n), G.one_f_one_b(P, n, reference_warmup=True)):
+        r = _check(sched, P, 1, n)
+        assert abs(r.max_bubble - S.ideal_bubble(P, n)) < 1e-9
+
+
+def test_1f1b_warmup_counts_match_reference_formula():
+    P, n = 4, 8
+    ref = G.one_f_one_b(P, n, reference_warmup=True)
+    txt = G.one_f_one_b(P, n)
+    for r in range(P):
+        lead_ref = next(i for i, a in enumerate(ref[r]) if a.op == Op.B)
+        lead_txt = next(i for i, a in enumerate(txt[r]) if a.op == Op.B)
+        assert lead_ref == min(n, 2 * (P - r - 1)) + 1
+        assert lead_txt == min(n, P - r - 1) + 1
+    r_ref, r_txt = _check(ref, P, 1, n), _check(txt, P, 1, n)
+    assert r_ref.peak_in_flight[0] > r_txt.peak_in_flight[0]
+
+
+@pytest.mark.parametrize("P,v,n", [(2, 2, 4), (4, 2, 8), (8, 2, 32), (1, 2, 4)])
+def test_interleaved_bubble_and_warmup(P, v, n):
+    sched = G.interleaved_1f1b(P, v, n)
+    r = _check(sched, P, v, n)
+    assert abs(r.max_bubble - S.ideal_bubble(P, n, v)) < 1e-9
+    for rank in range(P):
+        first_b = next(i for i, a in enumerate(sched[rank]) if a.op == Op.B)
+        assert first_b == min((v - 1) * P + 2 * ((P - 1) - rank), v * n) + 1
+        assert {a.stage for a in sched[rank]} == {rank + k * P for k in range(v)}
+
+
+def test_interleaved_rejects_bad_microbatch_count():
+    with pytest.raises(ValueError):
+        G.interleaved_1f1b(4, 2, 6)
+    with pytest.raises(ValueError):
+        G.zero_bubble(4, 2, 6)
+
+
+@pytest.mark.parametrize("P,v,n", [(4, 1, 8), (4, 2, 8), (8, 2, 32), (2, 1, 4)])
+def test_zero_bubble_beats_1f1b_and_bounds_memory(P, v, n):
+    zb = _check(G.zero_bubble(P, v, n), P, v, n)
+    base = _check(G.interleaved_1f1b(P, v, n) if v > 1 else G.one_f_one_b(P, n), P, v, n)
+    assert zb.makespan < base.makespan
+    assert zb.max_bubble < base.max_bubble
+    for r in range(P):
+        assert zb.peak_in_flight[r] <= (v - 1) * P + (P - 1 - r) + 1
+
+
+def test_looped_bfs_order():
+    sched = G.looped_bfs(2, 2, 3)
+    assert [str(a) for a in sched[0][:6]] == ["0F0", "0F1", "0F2", "2F0", "2F1", "2F2"]
+    assert [str(a) for a in sched[0][6:]] == ["2B0", "2B1", "2B2", "0B0", "0B1", "0B2"]
+    _check(sched, 2, 2, 3)
+
+
+def test_send_recv_pairing_is_consistent_between_neighbours():
+    P, v, n = 4, 2, 8
+    full = A.add_send_recv(G.zero_bubble(P, v, n), lambda s: s % P, P * v)
+    # the k-th transfer a rank sends to a peer is the k-th that peer receives from it
+    for r in range(P):
+        for peer in range(P):
+            sent = [(a.op, a.stage, a.mb) for a in full[r]
+                    if a.op in (Op.SEND_F, Op.SEND_B)
+                    and ((a.stage + (1 if a.op == Op.SEND_F else -1)) % P == peer)]
+            got = [(a.op, a.peer, a.mb) for a in full[peer]
+                   if a.op in (Op.RECV_F, Op.RECV_B) and (a.peer % P == r)]
+            assert [(s[1], s[2]) for s in sent] == [(g[1], g[2]) for g in got]
+
+
+def test_infeasible_order_is_reported():
+    bad = {0: [Action(0, Op.B, 0), Action(0, Op.F, 0)], 1: [Action(1, Op.F, 0), Action(1, Op.B, 0)]}
+    with pytest.raises(A.ScheduleDeadlock):
+        A.add_send_recv(bad, lambda s: s, 2)
+
+
+def test_csv_roundtrip_and_parse(tmp_path):
+    sched = A.add_send_recv(G.zero_bubble(2, 2, 4), lambda s: s % 2, 4)
+    path = os.path.join(tmp_path, "s.csv")
+    A.dump_csv(sched, path)
+    assert A.load_csv(path) == sched
+    assert Action.parse("3RECV_F7@2") == Action(3, Op.RECV_F, 7, 2)
+    assert str(Action(1, Op.REDUCE_GRAD)) == "1REDUCE_GRAD"
+    with pytest.raises(ValueError):
+        Action.parse("F3")
+
+
+def test_skip_connection_topology_in_comm_planning():
+    # stage 0 feeds stages 1 and 3
+    dests = {0: [1, 3], 1: [2], 2: [3], 3: []}
+    full = A.add_send_recv(G.gpipe(4, 2), lambda s: s, 4, dests)
+    assert Action(3, Op.RECV_F, 0, peer=0) in full[3] and Action(3, Op.RECV_F, 0, peer=2) in full[3]
+    assert Action(0, Op.RECV_B, 1, peer=3) in full[0] and Action(0, Op.RECV_B, 1, peer=1) in full[0]
+    S.simulate(full, lambda s: s, 4, dests=dests)
+
+
+def test_reduce_grad_placed_after_last_weight_action():
+    sched = G.with_reduce_grad(G.zero_bubble(2, 1, 4))
+    for r, acts in sched.items():
+        idx = [i for i, a in enumerate(acts) if a.op == Op.REDUCE_GRAD]
+        assert len(idx) == 1
+        assert all(a.op not in (Op.W, Op.B) for a in acts[idx[0] + 1:])
