@@ -35,23 +35,10 @@ struct BwdParams {
 
 constexpr int BR = 128;  // resident rows
 constexpr int BS = 64;   // streamed rows per block
-
-// Named barrier over `nthreads` threads that also ORs a predicate, so every participant takes the same branch.
-__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.or.pred p, %2, %3, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(out)
-      : "r"((uint32_t)pred), "r"(id), "r"(nthreads)
-      : "memory");
-  return out != 0;
-}
+constexpr int NST = 3;   // stages of the streamed operands (TMA latency hides behind two blocks of MMAs)
 
 template <int D, int kMode>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
               const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2, BwdParams p) {
   constexpr int NCH = D / 64;
@@ -65,20 +52,20 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sX1 = smem;
   uint8_t* sX2 = sX1 + RES_BYTES;
-  uint8_t* sY1 = sX2 + RES_BYTES;      // 2 stages
-  uint8_t* sY2 = sY1 + 2 * STR_BYTES;  // 2 stages
-  uint8_t* sP = sY2 + 2 * STR_BYTES;
-  uint8_t* sdS = sP + PS_BYTES;
-  float* s_lse = reinterpret_cast<float*>(sdS + PS_BYTES);  // [2][64]
+  uint8_t* sY1 = sX2 + RES_BYTES;        // NST stages
+  uint8_t* sY2 = sY1 + NST * STR_BYTES;  // NST stages
+  uint8_t* sP = sY2 + NST * STR_BYTES;   // 2 buffers
+  uint8_t* sdS = sP + 2 * PS_BYTES;   // 2 buffers
+  float* s_lse = reinterpret_cast<float*>(sdS + 2 * PS_BYTES);  // [2][64]
   float* s_delta = s_lse + 128;                             // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 128);
   uint64_t* res_full = bars;
-  uint64_t* y_full = bars + 1;
-  uint64_t* y_empty = bars + 3;
-  uint64_t* t_full = bars + 5;
-  uint64_t* ds_ready = bars + 7;
-  uint64_t* pds_free = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* y_full = bars + 1;           // [NST]
+  uint64_t* y_empty = bars + 1 + NST;    // [NST]
+  uint64_t* t_full = bars + 1 + 2 * NST;  // [2]
+  uint64_t* ds_ready = t_full + 2;       // [2]
+  uint64_t* pds_free = ds_ready + 2;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pds_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -114,13 +101,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(res_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NST; ++i) {
       mbar_init(&y_full[i], 1);
       mbar_init(&y_empty[i], 1);
-      mbar_init(&t_full[i], 1);
     }
-    mbar_init(ds_ready, 128);
-    mbar_init(pds_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&ds_ready[i], 256);
+      mbar_init(&pds_free[i], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -144,8 +133,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
         tma_load_2d(sX2 + c * CH_A, &tmX2, res_full, head_res * D + c * 64, row_base + r0);
       }
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(&y_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const int s = it % NST;
+        if (!mbar_wait(&y_empty[s], ((it / NST) & 1) ^ 1, abort_flag)) { ok = false; break; }
         int head_str, blk;
         if (kMode == 0) {
           head_str = hkv * G + it / nblk_per_head;
@@ -170,8 +159,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
       bool ok = true;
       auto issue_scores = [&](int it) {
         const int s = it & 1;
+        const int ys = it % NST;
         const uint32_t x1 = smem_u32(sX1), x2 = smem_u32(sX2);
-        const uint32_t y1 = smem_u32(sY1 + s * STR_BYTES), y2 = smem_u32(sY2 + s * STR_BYTES);
+        const uint32_t y1 = smem_u32(sY1 + ys * STR_BYTES), y2 = smem_u32(sY2 + ys * STR_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t oa = (kk >> 2) * CH_A + (kk & 3) * 32;
@@ -196,36 +186,40 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         if (it + 1 < n_it) {
-          if (!mbar_wait(&y_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&y_full[(it + 1) % NST], ((it + 1) / NST) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           issue_scores(it + 1);
         }
-        if (!mbar_wait(ds_ready, it & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&ds_ready[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t y1 = smem_u32(sY1 + s * STR_BYTES), y2 = smem_u32(sY2 + s * STR_BYTES);
+        const int ys = it % NST;
+        const uint32_t y1 = smem_u32(sY1 + ys * STR_BYTES), y2 = smem_u32(sY2 + ys * STR_BYTES);
         // in mode 0 a new query head restarts nothing: dK/dV accumulate over every head of the group
         if (kMode == 0) {
-          const uint32_t pa = smem_u32(sP);
+          const uint32_t pa = smem_u32(sP + s * PS_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BS / 16; ++kk)
             umma_ss<1>(tAccA, make_smem_desc(pa + kk * 32, 16, 1024), make_smem_desc(y2 + kk * 2048, CH_B, 1024),
                        idesc_acc, (it | kk) != 0);
         }
-        const uint32_t da = smem_u32(sdS);
+        const uint32_t da = smem_u32(sdS + s * PS_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk)
           umma_ss<1>(tAccB, make_smem_desc(da + kk * 32, 16, 1024), make_smem_desc(y1 + kk * 2048, CH_B, 1024),
                      idesc_acc, (it | kk) != 0);
-        umma_commit(&y_empty[s]);
-        umma_commit(pds_free);
+        umma_commit(&y_empty[ys]);
+        umma_commit(&pds_free[s]);
       }
       if (!ok) atomicExch(p.err, ERR_WAIT_TIMEOUT);
     }
   } else {
     // ------------------------------------------------------------ softmax-gradient threads, one resident row each
+    // 8 warps: two per TMEM lane quarter, each taking 32 of the block's 64 columns, so every scheduler has two
+    // warps to switch between while one waits on TMEM or the special-function unit
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const int tid = threadIdx.x - 64;  // 0..127
+    const int tid = threadIdx.x - 64;  // 0..255
     const int res_idx = r0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const int sw = r & 7;
@@ -250,13 +244,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
           val = (tid < 64) ? p.lse[off] * 1.4426950408889634f : p.delta[off];
         }
         if (tid < 64) s_lse[s * 64 + tid] = val;
-        else s_delta[s * 64 + (tid - 64)] = val;
+        else if (tid < 128) s_delta[s * 64 + (tid - 64)] = val;
       } else {
         blk = it;
       }
       const int c0 = blk * BS;
       bool got = mbar_wait(&t_full[s], (it >> 1) & 1, abort_flag);
-      if (kMode == 0) got = !named_bar_or(1, 128, !got);  // also publishes s_lse / s_delta
+      if (kMode == 0) got = !named_bar_or(1, 256, !got);  // also publishes s_lse / s_delta
       if (!got) { ok = false; break; }
       __syncwarp();
       tc_fence_after_sync();
@@ -264,28 +258,32 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
       if (kMode == 0) need_mask = (p.causal && (c0 < r0 + BR - 1)) || (c0 + BS > p.S) || (r0 + BR > p.S);
       else need_mask = (p.causal && (c0 + BS - 1 > r0)) || (c0 + BS > p.S) || (r0 + BR > p.S);
 
-      uint32_t pk_p[32], pk_ds[32];  // 64 bf16 each
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pk_p[16], pk_ds[16];  // 32 bf16 each: this warp's half of the block's columns
+      {
         uint32_t t1[32], t2[32];
-        tmem_ld_32x32(tT1 + s * 64 + lane_off + c * 32, t1);
-        tmem_ld_32x32(tT2 + s * 64 + lane_off + c * 32, t2);
+        tmem_ld_32x32(tT1 + s * 64 + lane_off + half * 32, t1);
+        tmem_ld_32x32(tT2 + s * 64 + lane_off + half * 32, t2);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
+        for (int e = 0; e < 32; e += 4) {
+          float lse4[4], dl4[4];
+          if (kMode == 0) {
+            const float4 a = *reinterpret_cast<const float4*>(&s_lse[s * 64 + half * 32 + e]);
+            const float4 d4 = *reinterpret_cast<const float4*>(&s_delta[s * 64 + half * 32 + e]);
+            lse4[0] = a.x; lse4[1] = a.y; lse4[2] = a.z; lse4[3] = a.w;
+            dl4[0] = d4.x; dl4[1] = d4.y; dl4[2] = d4.z; dl4[3] = d4.w;
+          } else {
 #pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            const int col = c * 32 + e + w;
-            float lse2, dl;
-            if (kMode == 0) {
-              lse2 = s_lse[s * 64 + col];
-              dl = s_delta[s * 64 + col];
-            } else {
-              lse2 = my_lse2;
-              dl = my_delta;
+            for (int w = 0; w < 4; ++w) {
+              lse4[w] = my_lse2;
+              dl4[w] = my_delta;
             }
-            float pr = exp2f(__uint_as_float(t1[e + w]) * p.scale_log2 - lse2);
+          }
+          float pv[4], dv[4];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const int col = half * 32 + e + w;
+            float pr = exp2f(__uint_as_float(t1[e + w]) * p.scale_log2 - lse4[w]);
             if (need_mask) {
               const int str_idx = c0 + col;
               const int qi = (kMode == 0) ? str_idx : res_idx;
@@ -294,33 +292,36 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
               pr = valid ? pr : 0.f;
             }
             pv[w] = pr;
-            dv[w] = pr * (__uint_as_float(t2[e + w]) - dl) * p.scale;
+            dv[w] = pr * (__uint_as_float(t2[e + w]) - dl4[w]) * p.scale;
           }
-          __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]);
-          __nv_bfloat162 d = __floats2bfloat162_rn(dv[0], dv[1]);
-          pk_p[c * 16 + e / 2] = *reinterpret_cast<uint32_t*>(&a);
-          pk_ds[c * 16 + e / 2] = *reinterpret_cast<uint32_t*>(&d);
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(pv[0], pv[1]), a1 = __floats2bfloat162_rn(pv[2], pv[3]);
+          __nv_bfloat162 d0 = __floats2bfloat162_rn(dv[0], dv[1]), d1 = __floats2bfloat162_rn(dv[2], dv[3]);
+          pk_p[e / 2] = *reinterpret_cast<uint32_t*>(&a0);
+          pk_p[e / 2 + 1] = *reinterpret_cast<uint32_t*>(&a1);
+          pk_ds[e / 2] = *reinterpret_cast<uint32_t*>(&d0);
+          pk_ds[e / 2 + 1] = *reinterpret_cast<uint32_t*>(&d1);
         }
       }
-      if (it > 0) {
-        // the accumulation GEMMs of the previous block must be done reading the P / dS tiles
-        if (!mbar_wait(pds_free, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      if (it >= 2) {
+        // the accumulation GEMMs that read this P / dS buffer two blocks ago must be done
+        if (!mbar_wait(&pds_free[s], ((it - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int unit = u ^ sw;
+      for (int u = 0; u < 4; ++u) {
+        const int unit = (half * 4 + u) ^ sw;
         if (kMode == 0)
-          *reinterpret_cast<uint4*>(sP + r * 128 + unit * 16) =
+          *reinterpret_cast<uint4*>(sP + s * PS_BYTES + r * 128 + unit * 16) =
               make_uint4(pk_p[u * 4], pk_p[u * 4 + 1], pk_p[u * 4 + 2], pk_p[u * 4 + 3]);
-        *reinterpret_cast<uint4*>(sdS + r * 128 + unit * 16) =
+        *reinterpret_cast<uint4*>(sdS + s * PS_BYTES + r * 128 + unit * 16) =
             make_uint4(pk_ds[u * 4], pk_ds[u * 4 + 1], pk_ds[u * 4 + 2], pk_ds[u * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(ds_ready);
+      mbar_arrive(&ds_ready[s]);
     }
     if (ok && n_it > 0) {
-      if (!mbar_wait(pds_free, (n_it - 1) & 1, abort_flag)) ok = false;
+      // commits complete in order, so the last block's barrier covers every accumulation GEMM
+      if (!mbar_wait(&pds_free[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) ok = false;
     }
     __syncwarp();
     if (ok) {
@@ -331,7 +332,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
         const uint32_t tA = (which == 0 ? tAccA : tAccB) + lane_off;
         __nv_bfloat16* base = (which == 0 ? p.out_a : p.out_b);
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;  // each half writes its own D/2 columns
           uint32_t v[32];
           if (n_it > 0) {
             tmem_ld_32x32(tA + c * 32, v);
@@ -398,7 +400,7 @@ template <int D, int kMode>
 static int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2,
                       const BwdParams& p, cudaStream_t stream) {
   constexpr int NCH = D / 64;
-  constexpr int SMEM = 2 * NCH * 128 * 128 + 4 * NCH * 64 * 128 + 2 * 128 * 128 + 1024 + 1024 + 256;
+  constexpr int SMEM = 2 * NCH * 128 * 128 + 2 * NST * NCH * 64 * 128 + 4 * 128 * 128 + 1024 + 1024 + 256;
   auto kern = fa_bwd_kernel<D, kMode>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -407,7 +409,7 @@ static int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtens
     attr_set = true;
   }
   dim3 grid((p.S + BR - 1) / BR, kMode == 0 ? p.Hkv : p.Hq, p.B);
-  kern<<<grid, 192, SMEM, stream>>>(x1, x2, y1, y2, p);
+  kern<<<grid, 320, SMEM, stream>>>(x1, x2, y1, y2, p);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

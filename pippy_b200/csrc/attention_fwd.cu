@@ -5,9 +5,12 @@
 //   softmax            one thread per query row reads its S row from TMEM (no shuffles), writes bf16 P
 //                      into swizzled smem
 //   O_j = P V          tcgen05.mma, V is the MN-major operand straight from its TMA tile
-// S and O_j are double-buffered in TMEM so S(j+1) runs during softmax(j) and P V(j) during the
-// accumulation of O_{j-1}; the running output lives in registers (128 fp32 per thread).
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (+TMEM owner), 2..5 = softmax/epilogue.
+// S is double-buffered in TMEM and P in shared memory, so S(j+1) runs during softmax(j) and P V(j) during
+// softmax(j+1).  O accumulates in TMEM across KV blocks; it is only rescaled when some row's running maximum grew
+// by more than 2^8 (the stale maximum keeps every probability <= 256, exact after the final division by l).
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (+TMEM owner), 2..9 = softmax/epilogue: two warps per TMEM lane
+// quarter, each owning 64 of the block's 128 columns (row maxima are exchanged through shared memory), so every
+// scheduler has two warps to alternate between.
 #include "tc05.cuh"
 
 #include <math_constants.h>
@@ -33,7 +36,7 @@ constexpr int BM = 128;
 constexpr int BN = 128;
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, FwdParams p) {
   constexpr int NCH = D / 64;               // 64-column chunks per operand tile
@@ -41,13 +44,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr int TILE_BYTES = NCH * CHUNK_BYTES;
   constexpr int P_BYTES = 2 * CHUNK_BYTES;  // 128 x 128 bf16
 
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (smem != smem_raw) {
+    // the launch reserves no slack for re-alignment; refuse to run rather than overrun shared memory
+    if (threadIdx.x == 0) atomicExch(p.err, ERR_BAD_ARG);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
   uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint8_t* sP = sV + 2 * TILE_BYTES;  // 2 buffers
+  float* s_xchg = reinterpret_cast<float*>(sP + 2 * P_BYTES);  // [2 buffers][2 halves][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_xchg + 512);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* k_empty = bars + 3;
@@ -56,7 +65,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* s_full = bars + 9;
   uint64_t* o_full = bars + 11;
   uint64_t* p_ready = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -80,8 +89,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&o_full[i], 1);
+      mbar_init(&p_ready[i], 256);
     }
-    mbar_init(p_ready, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -90,8 +99,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS0 = tmem_base;        // S buffers: columns [0,128) and [128,256)
-  const uint32_t tO0 = tmem_base + 256;  // O buffers: columns [256,256+D) and [384,384+D)
+  const uint32_t tS0 = tmem_base;       // S buffers: columns [0,128) and [128,256)
+  const uint32_t tO = tmem_base + 256;  // O accumulator: columns [256, 256 + D)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -145,14 +154,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           tc_fence_after_sync();
           issue_s(j + 1);
         }
-        if (!mbar_wait(p_ready, j & 1, abort_flag) || !mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[s], ph, abort_flag) || !mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * TILE_BYTES);
+        const uint32_t pa = smem_u32(sP + s * P_BYTES), va = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t da = make_smem_desc(pa + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc(va + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss<1>(tO0 + s * 128, da, db, idesc_pv, kk != 0);
+          umma_ss<1>(tO, da, db, idesc_pv, (j | kk) != 0);
         }
         umma_commit(&o_full[s]);
         umma_commit(&v_empty[s]);
@@ -160,117 +169,116 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (!ok) atomicExch(p.err, ERR_WAIT_TIMEOUT);
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (one row per thread)
+    // ------------------------------------------------------------ softmax + epilogue (row x column half per thread)
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
     const int q_idx = q0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-    float m = -CUDART_INF_F, l = 0.f, alpha_pending = 0.f;
+    float m = -CUDART_INF_F, l = 0.f;  // l: this thread's half of the row sum
     bool ok = true;
-    uint8_t* p_row = sP + r * 128;
     const int sw = r & 7;
 
     for (int j = 0; j < nblk; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      bool got = mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag);
       __syncwarp();
       tc_fence_after_sync();
       const int k0 = j * BN;
+      const int col0 = half * 64;
       const bool need_mask = (p.causal && (k0 + BN - 1 > q0)) || (k0 + BN > p.S);
-      const uint32_t tS = tS0 + s * 128 + lane_off;
-      // pass 1: row maximum
+      const uint32_t tS = tS0 + s * 128 + lane_off + col0;
+      uint32_t v[2][32];
+      tmem_ld_32x32(tS, v[0]);
+      tmem_ld_32x32(tS + 32, v[1]);
+      tmem_ld_wait();
       float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const int kv = k0 + c * 32 + e;
+            const int kv = k0 + col0 + c * 32 + e;
             const bool valid = (kv < p.S) && (!p.causal || kv <= q_idx);
-            mx = fmaxf(mx, valid ? __uint_as_float(v[e]) : -CUDART_INF_F);
+            if (!valid) v[c][e] = 0xff800000u;  // -inf
+            mx = fmaxf(mx, __uint_as_float(v[c][e]));
           }
-        } else {
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[c][e]));
+      }
+      // combine with the other half of the row
+      s_xchg[(s * 2 + half) * 128 + r] = mx;
+      got = !named_bar_or(1, 256, !got);
+      if (!got) { ok = false; break; }
+      mx = fmaxf(mx, s_xchg[(s * 2 + (half ^ 1)) * 128 + r]);
+      const float m_cand = fmaxf(m, mx * p.scale_log2);
+      // rescale only when some row of the warp moved its maximum by more than 2^8
+      const bool grow = m_cand > m + 8.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_use = (m_cand == -CUDART_INF_F) ? 0.f : m_cand;
+        const float alpha = exp2f(m - m_use);  // 0 on the first block (m = -inf)
+        if (j > 0) {
+          if (!mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          __syncwarp();
+          tc_fence_after_sync();
+#pragma unroll
+          for (int cc = 0; cc < D / 64; ++cc) {
+            const uint32_t ta = tO + lane_off + (half * (D / 64) + cc) * 32;
+            uint32_t o[32];
+            tmem_ld_32x32(ta, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_32x32(ta, o);
+          }
+          tmem_st_wait();
         }
+        l *= alpha;
+        m = m_use;
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
-      const float alpha = exp2f(m - m_use);
-      if (j > 0) {
-        // P V(j-1) finished: the P buffer is free again and O_{j-1} is in TMEM
-        if (!mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-        __syncwarp();
-        tc_fence_after_sync();
+      if (j >= 2) {
+        // the P buffer about to be overwritten was read by P V(j-2)
+        if (!mbar_wait(&o_full[s], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
       }
-      // pass 2: probabilities -> bf16 -> swizzled smem
+      uint8_t* p_row = sP + s * P_BYTES + half * CHUNK_BYTES + r * 128;
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        float pr[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m_use);
-          if (need_mask) {
-            const int kv = k0 + c * 32 + e;
-            const bool valid = (kv < p.S) && (!p.causal || kv <= q_idx);
-            x = valid ? x : 0.f;
-          }
-          pr[e] = x;
-          rowsum += x;
+      for (int u = 0; u < 8; ++u) {
+        uint4 w;
+        __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x0 = exp2f(__uint_as_float(v[u >> 2][(u & 3) * 8 + e * 2]) * p.scale_log2 - m);
+          const float x1 = exp2f(__uint_as_float(v[u >> 2][(u & 3) * 8 + e * 2 + 1]) * p.scale_log2 - m);
+          rowsum += x0 + x1;
+          wb[e] = __floats2bfloat162_rn(x0, x1);
         }
-        // 32 columns = 4 units of 16 B inside 64-column chunk (c / 2), units (c & 1) * 4 .. +3
-        uint8_t* chunk = p_row + (c >> 1) * CHUNK_BYTES;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) wb[e] = __floats2bfloat162_rn(pr[u * 8 + e * 2], pr[u * 8 + e * 2 + 1]);
-          const int unit = ((c & 1) * 4 + u) ^ sw;
-          *reinterpret_cast<uint4*>(chunk + unit * 16) = w;
-        }
+        *reinterpret_cast<uint4*>(p_row + ((u ^ sw) * 16)) = w;
       }
-      l = l * alpha + rowsum;
-      m = m_new;
+      l += rowsum;
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
-      if (j > 0) {
-        // fold O_{j-1} (relative to the previous maximum) into the running output
-        const uint32_t tO = tO0 + ((j - 1) & 1) * 128 + lane_off;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tO + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o_acc[c * 32 + e] = o_acc[c * 32 + e] * alpha_pending + __uint_as_float(v[e]);
-        }
-      }
-      alpha_pending = alpha;
+      mbar_arrive(&p_ready[s]);
     }
-    if (ok && nblk > 0) {
-      if (!mbar_wait(&o_full[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag)) ok = false;
-    }
+    bool got = true;
+    if (ok && nblk > 0) got = mbar_wait(&o_full[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag);
+    // total row sum = both halves
+    s_xchg[half * 128 + r] = l;
+    got = !named_bar_or(1, 256, !(got && ok));
+    if (!got) ok = false;
     __syncwarp();
     if (ok && nblk > 0) {
       tc_fence_after_sync();
-      const uint32_t tO = tO0 + ((nblk - 1) & 1) * 128 + lane_off;
-      const float inv_l = 1.f / l;
+      const float l_total = l + s_xchg[(half ^ 1) * 128 + r];
+      const float inv_l = 1.f / l_total;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tO + c * 32, v);
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;
+        uint32_t o[32];
+        tmem_ld_32x32(tO + lane_off + c * 32, o);
         tmem_ld_wait();
         if (q_idx < p.S) {
           __nv_bfloat16* dst = p.o + (long long)(row_base + q_idx) * p.o_stride + h * D + c * 32;
@@ -279,17 +287,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             uint4 w;
             __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i0 = u * 8 + e * 2;
-              const float a0 = (o_acc[c * 32 + i0] * alpha_pending + __uint_as_float(v[i0])) * inv_l;
-              const float a1 = (o_acc[c * 32 + i0 + 1] * alpha_pending + __uint_as_float(v[i0 + 1])) * inv_l;
-              wb[e] = __floats2bfloat162_rn(a0, a1);
-            }
+            for (int e = 0; e < 4; ++e)
+              wb[e] = __floats2bfloat162_rn(__uint_as_float(o[u * 8 + e * 2]) * inv_l,
+                                            __uint_as_float(o[u * 8 + e * 2 + 1]) * inv_l);
             reinterpret_cast<uint4*>(dst)[u] = w;
           }
         }
       }
-      if (q_idx < p.S) p.lse[((long long)b * p.Hq + h) * p.S + q_idx] = (m + log2f(l)) * 0.6931471805599453f;
+      if (half == 0 && q_idx < p.S)
+        p.lse[((long long)b * p.Hq + h) * p.S + q_idx] = (m + log2f(l_total)) * 0.6931471805599453f;
     }
     if (!ok && lane == 0) atomicExch(p.err, ERR_WAIT_TIMEOUT);
   }
@@ -308,7 +314,7 @@ template <int D>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                       cudaStream_t stream) {
   constexpr int TILE = (D / 64) * 128 * 128;
-  constexpr int SMEM = 5 * TILE + 2 * 128 * 128 + 1024 + 256;
+  constexpr int SMEM = 5 * TILE + 2 * (2 * 128 * 128) + 2048 + 256;
   auto kern = fa_fwd_kernel<D>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -317,7 +323,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     attr_set = true;
   }
   dim3 grid((p.S + BM - 1) / BM, p.Hq, p.B);
-  kern<<<grid, 192, SMEM, stream>>>(tq, tk, tv, p);
+  kern<<<grid, 320, SMEM, stream>>>(tq, tk, tv, p);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
