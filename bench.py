@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--microbatches", type=int, default=32)
     ap.add_argument("--virtual", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sm-reserve", type=int, default=None,
+                    help="SMs kept out of the GEMM grid for communication kernels (default: 0 on 1 GPU, 8 otherwise)")
     ap.add_argument("--timing", action="store_true", help="also report the measured bubble of the last step")
     return ap.parse_args()
 
@@ -145,6 +147,10 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    from pippy_b200.ops.gemm import set_sm_reserve
+
+    sm_reserve = args.sm_reserve if args.sm_reserve is not None else (0 if world == 1 else 8)
+    set_sm_reserve(sm_reserve)
     cfg, model_desc = model_config(args.model)
     schedule = args.schedule or ("interleaved_1f1b" if world == 1 else "zero_bubble")
     virtual = args.virtual
@@ -213,6 +219,11 @@ def main() -> None:
     bubble = None
     if args.timing and pipe.schedule.last_step_stats is not None:
         bubble = max_over_ranks(pipe.schedule.last_step_stats["bubble"])
+        dump_dir = os.environ.get("PIPPY_TIMELINE_DIR")
+        if dump_dir:
+            os.makedirs(dump_dir, exist_ok=True)
+            with open(os.path.join(dump_dir, f"timeline_rank{rank}.json"), "w") as f:
+                json.dump(pipe.schedule.last_step_stats, f)
 
     # ---------------------------------------------------------------- end-to-end region (H2D inputs + D2H loss each step)
     e2e = None
@@ -246,6 +257,7 @@ def main() -> None:
         }
         _lib.check_device_errors()
 
+    peak_mem = max_over_ranks(torch.cuda.max_memory_allocated() / 2**30)
     if rank == 0:
         tokens = args.batch * args.seq * args.steps
         value = tokens / (ms_total * 1e-3)
@@ -272,6 +284,7 @@ def main() -> None:
                 "microbatches": args.microbatches,
                 "parallelism": f"pp{world}" + (f"x{virtual}v" if virtual > 1 else ""),
                 "schedule": schedule,
+                "sm_reserve": sm_reserve,
                 "optimizer": "AdamW lr 3e-4 (fused, fp32 moments, fp32 gradient accumulation)",
                 "l2": "inputs larger than L2 (13.5 GB of weights and GBs of activations stream every step)",
             },
@@ -280,6 +293,7 @@ def main() -> None:
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": int(launches),
+            "peak_mem_gb_max_rank": peak_mem,
         }
         if bubble is not None:
             out["bubble_measured"] = bubble

@@ -127,11 +127,17 @@ class DeferredWeightGrads:
             fn()
 
 
-_tls = threading.local()
+# Process-wide on purpose: autograd runs the backward of CUDA ops on its own device thread, so a thread-local set by
+# the caller would be invisible there.  The schedule runs one action at a time, so a single slot is enough.
+class _DeferralState:
+    queue: Optional["DeferredWeightGrads"] = None
+
+
+_tls = _DeferralState
 
 
 def current_deferral() -> Optional[DeferredWeightGrads]:
-    return getattr(_tls, "queue", None)
+    return _tls.queue
 
 
 class defer_weight_grads:
@@ -141,7 +147,7 @@ class defer_weight_grads:
         self.queue = queue
 
     def __enter__(self):
-        self.prev = getattr(_tls, "queue", None)
+        self.prev = _tls.queue
         _tls.queue = self.queue
         return self.queue
 
@@ -214,7 +220,15 @@ def stage_backward_input(
     # parameters whose owning op writes their gradient itself (ops.functional) never go through the graph walk
     weights = [w for w in weights if w.requires_grad and not getattr(w, "_pb_direct_grad", False)]
     if not diff_inputs:
-        plan.full_backward = (outs, grads)
+        # First stage: nobody waits for an input gradient, but the chain of activation gradients still has to run
+        # to reach the early layers' parameters.  Run it now with deferral on: layers of this package queue their
+        # weight-gradient GEMMs for the W action (so I and W cost about what they cost on every other stage, which
+        # keeps the schedule balanced); parameters of other ops simply get their gradient during this pass.
+        if outs:
+            queue = DeferredWeightGrads()
+            plan.deferred = queue
+            with defer_weight_grads(queue):
+                torch.autograd.backward(outs, grad_tensors=grads)
         return [None] * len(input_values), plan
     if not outs:
         return [None] * len(input_values), plan
@@ -318,9 +332,13 @@ def stage_backward_input(
 
     for node, _params in split_nodes:
         handles.append(node.register_prehook(make_hook(node)))
+    # The graph has to survive only if the weight half will re-enter it; when every parameter gradient is deferred
+    # through the queue (the package's own layers) the saved activations are released as the input pass consumes them.
+    keep_graph = bool(split_nodes) or bool(weight_only_outputs)
     try:
         with defer_weight_grads(queue):
-            in_grads = torch.autograd.grad(outs, diff_inputs, grad_outputs=grads, retain_graph=True, allow_unused=True)
+            in_grads = torch.autograd.grad(outs, diff_inputs, grad_outputs=grads, retain_graph=keep_graph,
+                                           allow_unused=True)
     finally:
         for h in handles:
             h.remove()

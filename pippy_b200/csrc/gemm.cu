@@ -410,7 +410,13 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
 
 }  // namespace pb
 
+static int g_sm_reserve = 0;
+
 extern "C" {
+
+// Leaves `n` SMs out of the persistent GEMM grid (for communication kernels that must run beside it).
+void pb_set_sm_reserve(int n) { g_sm_reserve = n < 0 ? 0 : n; }
+int pb_get_sm_reserve() { return g_sm_reserve; }
 
 // C[M,N] = A.B^T with fused epilogue.  A: a_mn ? [K, M] (ld = lda) : [M, K];  B: b_mn ? [K, N] : [N, K].
 // variant: 0 = automatic, 1 = single-CTA tiles (128 x 256), 2 = CTA-pair tiles (256 x 256),
@@ -461,10 +467,12 @@ int pb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   p.a_mn = a_mn;
   p.b_mn = b_mn;
   p.err = err_dev;
+  int sms = sm_count - g_sm_reserve;
+  if (sms < 2) sms = 2;
   switch (variant) {
-    case 1: return launch_gemm<1, 256, 4>(tmA, tmB, p, sm_count, stream);
-    case 2: return launch_gemm<2, 256, 6>(tmA, tmB, p, sm_count, stream);
-    case 3: return launch_gemm<1, 128, 6>(tmA, tmB, p, sm_count, stream);
+    case 1: return launch_gemm<1, 256, 4>(tmA, tmB, p, sms, stream);
+    case 2: return launch_gemm<2, 256, 6>(tmA, tmB, p, sms, stream);
+    case 3: return launch_gemm<1, 128, 6>(tmA, tmB, p, sms, stream);
     default: return -5;
   }
 }

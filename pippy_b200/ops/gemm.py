@@ -62,3 +62,9 @@ def gemm(
     )
     _lib.check(rc, "pb_gemm_bf16")
     return out
+
+
+def set_sm_reserve(n: int) -> None:
+    """Keeps ``n`` SMs out of the persistent GEMM grid so that communication kernels (NCCL point-to-point, the
+    fused collectives of this package) always find a free SM while a GEMM is running."""
+    _lib.lib().pb_set_sm_reserve(_lib.c_int(int(n)))

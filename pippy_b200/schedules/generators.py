@@ -115,13 +115,14 @@ def zero_bubble(
     n_mb: int,
     max_pending_w: Optional[int] = None,
     extra_in_flight: int = 0,
-    cost_f: int = 1,
-    cost_i: int = 1,
-    cost_w: int = 1,
+    cost_f: int = 2,
+    cost_i: int = 3,
+    cost_w: int = 2,
 ) -> Schedule:
     """Zero-bubble schedule with the backward split into I (input grads) and W (weight grads).
 
-    Built by list scheduling on a unit-cost timeline: each rank visits forwards and input-gradient passes in the
+    Built by list scheduling on a timeline with costs F:I:W (default 2:3:2, a transformer layer whose input-gradient
+    pass carries the attention backward): each rank visits forwards and input-gradient passes in the
     interleaved-1F1B orders, always prefers a ready I, then a ready F while fewer than
     ``(v-1)*P + (P-1-r) + 1 + extra_in_flight`` microbatch-stages are in flight, and fills every remaining gap
     with the oldest deferred W (``max_pending_w`` bounds how many weight-gradient passes may be parked, and with

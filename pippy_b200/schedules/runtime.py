@@ -41,13 +41,14 @@ def sorted_batch_isend_irecv(p2p_ops: List[dist.P2POp]) -> Dict[int, Any]:
     """Issues the ops grouped by peer, peers in ascending order, one batch per peer; returns ``{peer: work}``.
     A fixed issue order across ranks avoids deadlocks when a stage talks to several peers (skip connections)
     (reference PipelineSchedule.py:200-222)."""
-    by_peer: Dict[int, List[dist.P2POp]] = defaultdict(list)
+    by_peer: Dict[Any, List[dist.P2POp]] = defaultdict(list)
     for op in p2p_ops:
-        by_peer[op.peer].append(op)
-    works: Dict[int, Any] = {}
-    for peer in sorted(by_peer):
-        reqs = dist.batch_isend_irecv(by_peer[peer])
-        works[peer] = reqs[-1] if len(reqs) == 1 else _WorkGroup(reqs)
+        by_peer[(op.peer, id(op.group))].append(op)  # a batch must stay inside one process group
+    works: Dict[Any, Any] = {}
+    for key in sorted(by_peer, key=lambda k: k[0]):
+        reqs = dist.batch_isend_irecv(by_peer[key])
+        work = reqs[-1] if len(reqs) == 1 else _WorkGroup(reqs)
+        works[key[0] if key[0] not in works else key] = work
     return works
 
 
@@ -97,9 +98,11 @@ class _Timer:
             torch.cuda.synchronize()
             wall = self.t_begin.elapsed_time(self.t_end) * 1e-3
             durs = [(a, s.elapsed_time(e) * 1e-3) for a, s, e in self.records]
+            starts = [self.t_begin.elapsed_time(s) * 1e-3 for _, s, _ in self.records]
         else:
             wall = self.t_end - self.t_begin
             durs = [(a, e - s) for a, s, e in self.records]
+            starts = [s - self.t_begin for _, s, _ in self.records]
         busy = sum(d for _, d in durs)
         per_op: Dict[str, float] = defaultdict(float)
         for a, d in durs:
@@ -110,6 +113,7 @@ class _Timer:
             "bubble": (1.0 - busy / wall) if wall > 0 else 0.0,
             "per_op_s": dict(per_op),
             "actions": [(str(a), d) for a, d in durs],
+            "timeline": [(str(a), t0, t0 + d) for (a, d), t0 in zip(durs, starts)],
         }
 
 
@@ -128,6 +132,7 @@ class PipelineSchedule:
         grad_reducer: Optional[Any] = None,
         p2p_timeout_s: Optional[float] = None,
         record_timing: bool = False,
+        use_link_groups: bool = True,
     ):
         self._stages = sorted(stages, key=lambda s: s.stage_index)
         self._stage_by_index = {s.stage_index: s for s in self._stages}
@@ -154,6 +159,15 @@ class PipelineSchedule:
         for st in self._stages:
             st.has_backward = self._has_backward
             st._prepare_forward_infra(n_microbatches)
+        self.link_groups = None
+        if dist.is_available() and dist.is_initialized() and self.pp_group_size > 1 and use_link_groups:
+            from ..comm.p2p import LinkGroups, pipeline_links
+
+            links = pipeline_links(self.num_stages, self.pp_group_size, self._topology())
+            # communicators are expensive: stages built once keep theirs across schedule objects
+            self.link_groups = first.link_groups if first.link_groups is not None else LinkGroups(first.group, links)
+            for st in self._stages:
+                st.link_groups = self.link_groups
         self._actions: Optional[List[Action]] = None
         self.pipeline_order: Optional[Schedule] = None
         self.pipeline_order_with_comms: Optional[Schedule] = None

@@ -122,6 +122,7 @@ class PipelineStageBase:
         self.fwd_chunk_id = 0
         self.bwd_chunk_id = 0
         self._dp_wrapper_configured_last = True
+        self.link_groups = None  # comm.p2p.LinkGroups, installed by the schedule
 
     # ------------------------------------------------------------------ properties
     @property
@@ -142,6 +143,18 @@ class PipelineStageBase:
 
     def is_local_stage(self, stage: int) -> bool:
         return self.rank_of_stage(stage) == self.group_rank
+
+    def _link_group(self, producer_rank: int, consumer_rank: int, kind: str):
+        """Process group of the directed link producer -> consumer for forward ("F") transfers, or of the reverse
+        direction for gradient ("B") transfers; the pipeline group when no per-link groups were installed."""
+        if self.link_groups is not None:
+            if kind == "F":
+                g = self.link_groups.get(producer_rank, consumer_rank, "F")
+            else:
+                g = self.link_groups.get(consumer_rank, producer_rank, "B")
+            if g is not None:
+                return g
+        return self.group
 
     # ------------------------------------------------------------------ buffers
     def _prepare_forward_infra(self, num_microbatches: int) -> None:
@@ -188,8 +201,9 @@ class PipelineStageBase:
         for info in self.args_recv_info[mb]:
             if not isinstance(info, RecvInfo) or (source is not None and info.source != source):
                 continue
-            peer = self._global_rank(self.rank_of_stage(info.source))
-            ops.append(dist.P2POp(dist.irecv, info.buffer, peer, self.group))
+            src_rank = self.rank_of_stage(info.source)
+            peer = self._global_rank(src_rank)
+            ops.append(dist.P2POp(dist.irecv, info.buffer, peer, self._link_group(src_rank, self.group_rank, "F")))
         return ops
 
     def get_bwd_recv_ops(self, mb: Optional[int] = None, source: Optional[int] = None) -> List[dist.P2POp]:
@@ -200,22 +214,25 @@ class PipelineStageBase:
         for (_, dst), info in sorted(self._grad_recv_infos(mb).items()):
             if source is not None and dst != source:
                 continue
-            peer = self._global_rank(self.rank_of_stage(dst))
-            ops.append(dist.P2POp(dist.irecv, info.buffer, peer, self.group))
+            dst_rank = self.rank_of_stage(dst)
+            peer = self._global_rank(dst_rank)
+            ops.append(dist.P2POp(dist.irecv, info.buffer, peer, self._link_group(self.group_rank, dst_rank, "B")))
         return ops
 
     def get_fwd_send_ops(self, mb: Optional[int] = None) -> List[dist.P2POp]:
         """isend ops for every (output, remote consumer stage) of microbatch ``mb``, consumers ascending."""
         mb = (self.fwd_chunk_id - 1) if mb is None else mb
-        outputs = self.fwd_cache[mb][0] if mb in self.fwd_cache else self._sent_outputs[mb]
+        outputs = self._sent_outputs[mb]
         ops: List[Tuple[int, int, dist.P2POp]] = []
         for out_idx, consumers in self.output_dests.items():
             out = outputs[out_idx]
             for dst in consumers:
                 if self.is_local_stage(dst):
                     continue
-                peer = self._global_rank(self.rank_of_stage(dst))
-                ops.append((dst, out_idx, dist.P2POp(dist.isend, out.detach().contiguous(), peer, self.group)))
+                dst_rank = self.rank_of_stage(dst)
+                peer = self._global_rank(dst_rank)
+                ops.append((dst, out_idx, dist.P2POp(dist.isend, out.detach().contiguous(), peer,
+                                                     self._link_group(self.group_rank, dst_rank, "F"))))
         ops.sort(key=lambda t: (t[0], t[1]))
         return [op for _, _, op in ops]
 
@@ -236,8 +253,10 @@ class PipelineStageBase:
                 )
             if grad is None:
                 continue
-            peer = self._global_rank(self.rank_of_stage(spec.source))
-            ops.append((spec.source, idx, dist.P2POp(dist.isend, grad.contiguous(), peer, self.group)))
+            src_rank = self.rank_of_stage(spec.source)
+            peer = self._global_rank(src_rank)
+            ops.append((spec.source, idx, dist.P2POp(dist.isend, grad.contiguous(), peer,
+                                                     self._link_group(src_rank, self.group_rank, "B"))))
         for idx, grad in enumerate(grads):
             if grad is not None and idx < len(self.input_specs) and self.input_specs[idx].source is None:
                 pass  # gradient of a model input: nothing to send
@@ -324,12 +343,19 @@ class PipelineStageBase:
         if isinstance(output, list):
             output = tuple(output)
         output_tuple = output if isinstance(output, tuple) else (output,)
-        self.output_chunks[mb] = output
+        # what outlives the backward must not pin the autograd graph: keep detached views only
+        def _detached(o):
+            return o.detach() if isinstance(o, torch.Tensor) else o
+
+        if self.is_last:
+            self.output_chunks[mb] = (
+                tuple(_detached(o) for o in output) if isinstance(output, tuple) else _detached(output)
+            )
         flat_inputs = flatten_args(composite_args) + flatten_args(kwargs)
         self.fwd_cache[mb] = (output_tuple, flat_inputs)
         if not hasattr(self, "_sent_outputs"):
             self._sent_outputs: Dict[int, Tuple[Any, ...]] = {}
-        self._sent_outputs[mb] = output_tuple
+        self._sent_outputs[mb] = tuple(_detached(o) for o in output_tuple)
         self.fwd_chunk_id = mb + 1
         logger.debug("[%d] Forwarded chunk %d, outputs: %s", self.stage_index, mb, map_debug_info(output))
         return output
