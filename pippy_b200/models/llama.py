@@ -92,16 +92,25 @@ class LlamaMLP(nn.Module):
 
 
 class LlamaBlock(nn.Module):
-    def __init__(self, cfg: LlamaConfig, device=None, dtype=None):
+    """One decoder layer, or one half of it when a stage boundary falls between its attention and its MLP
+    (``has_attention`` / ``has_ffn``); parameter names are the same either way."""
+
+    def __init__(self, cfg: LlamaConfig, device=None, dtype=None, has_attention: bool = True, has_ffn: bool = True):
         super().__init__()
-        self.attention_norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device, dtype=dtype)
-        self.attention = LlamaAttention(cfg, device=device, dtype=dtype)
-        self.ffn_norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device, dtype=dtype)
-        self.feed_forward = LlamaMLP(cfg, device=device, dtype=dtype)
+        self.has_attention, self.has_ffn = has_attention, has_ffn
+        if has_attention:
+            self.attention_norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device, dtype=dtype)
+            self.attention = LlamaAttention(cfg, device=device, dtype=dtype)
+        if has_ffn:
+            self.ffn_norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device, dtype=dtype)
+            self.feed_forward = LlamaMLP(cfg, device=device, dtype=dtype)
 
     def forward(self, x, B: int, S: int):  # x: [B*S, dim]
-        x = self.attention(self.attention_norm(x), x, B, S)
-        return self.feed_forward(self.ffn_norm(x), x)
+        if self.has_attention:
+            x = self.attention(self.attention_norm(x), x, B, S)
+        if self.has_ffn:
+            x = self.feed_forward(self.ffn_norm(x), x)
+        return x
 
 
 def layer_range(n_layers: int, stage: int, num_stages: int) -> range:
@@ -111,18 +120,97 @@ def layer_range(n_layers: int, stage: int, num_stages: int) -> range:
     return range(start, start + base + (1 if stage < rem else 0))
 
 
+def unit_costs(cfg: LlamaConfig, seq_len: int):
+    """Relative cost of (attention half, MLP half, head, embedding), from forward FLOPs per token; attention
+    FLOPs count double (they run further from the tensor-core peak than the GEMMs) and the head carries the final
+    norm and the loss."""
+    d, hd = cfg.dim, cfg.head_dim
+    attn = 2.0 * d * (cfg.n_heads + 2 * cfg.kv_heads) * hd + 2.0 * d * d + 2.0 * (2.0 * seq_len * d)
+    ffn = 6.0 * d * cfg.ffn_dim
+    head = 2.0 * d * cfg.vocab_size * 1.35
+    return attn, ffn, head, 0.02 * (attn + ffn)
+
+
+def balanced_partition(cfg: LlamaConfig, num_stages: int, pp_size: int, seq_len: int = 4096):
+    """Cuts the sequence [embed, attn0, mlp0, attn1, mlp1, ..., head] into ``num_stages`` contiguous stages so that
+    the most loaded RANK (stage s lives on rank s % pp_size) carries as little as possible.  Boundaries may fall
+    between a layer's attention and MLP.  Returns, per stage, a list of ``(layer, has_attention, has_ffn)``.
+
+    With whole layers only, the head (worth most of a layer) always lands on top of a full share of layers; at
+    8 ranks x 2 stages that alone makes one rank 16 % slower than the rest."""
+    attn, ffn, head, embed = unit_costs(cfg, seq_len)
+    units = []  # (cost, layer, kind)
+    for i in range(cfg.n_layers):
+        units.append((attn, i, "a"))
+        units.append((ffn, i, "f"))
+    n = len(units)
+    if num_stages > n:
+        raise ValueError(f"{num_stages} stages for {cfg.n_layers} layers")
+    prefix = [0.0]
+    for c, _, _ in units:
+        prefix.append(prefix[-1] + c)
+
+    def stage_cost(bounds, s):
+        c = prefix[bounds[s + 1]] - prefix[bounds[s]]
+        if s == 0:
+            c += embed
+        if s == num_stages - 1:
+            c += head
+        return c
+
+    def max_rank_load(bounds):
+        loads = [0.0] * pp_size
+        for s in range(num_stages):
+            loads[s % pp_size] += stage_cost(bounds, s)
+        return max(loads), sum(l * l for l in loads)
+
+    total = prefix[-1] + head + embed
+    target = total / num_stages
+    bounds = [0]
+    for s in range(1, num_stages):
+        want = s * target - embed
+        # nearest unit boundary that keeps every stage non-empty
+        lo, hi = bounds[-1] + 1, n - (num_stages - s)
+        best = min(range(lo, hi + 1), key=lambda b: abs(prefix[b] - want))
+        bounds.append(best)
+    bounds.append(n)
+    improved = True
+    while improved:
+        improved = False
+        for s in range(1, num_stages):
+            for delta in (-1, 1):
+                cand = list(bounds)
+                cand[s] += delta
+                if not (cand[s - 1] < cand[s] < cand[s + 1]):
+                    continue
+                if max_rank_load(cand) < max_rank_load(bounds):
+                    bounds = cand
+                    improved = True
+    stages = []
+    for s in range(num_stages):
+        per_layer = {}
+        for _, layer, kind in units[bounds[s]:bounds[s + 1]]:
+            a, f = per_layer.get(layer, (False, False))
+            per_layer[layer] = (a or kind == "a", f or kind == "f")
+        stages.append([(layer, a, f) for layer, (a, f) in sorted(per_layer.items())])
+    return stages
+
+
 class LlamaStage(nn.Module):
-    """Layers ``layer_ids`` of the model, with the embedding if ``first`` and the norm + head if ``last``.
-    Input: token ids ``[B, S]`` (first stage) or hidden states ``[B, S, dim]``; output: hidden states
-    ``[B, S, dim]`` or logits ``[B, S, vocab]``."""
+    """A contiguous slice of the model: ``parts`` lists ``(layer, has_attention, has_ffn)``; the embedding goes with
+    ``first`` and the final norm + head with ``last``.  Input: token ids ``[B, S]`` (first stage) or hidden states
+    ``[B, S, dim]``; output: hidden states ``[B, S, dim]`` or logits ``[B, S, vocab]``."""
 
     def __init__(self, cfg: LlamaConfig, layer_ids, first: bool, last: bool, device=None, dtype=None):
         super().__init__()
         self.cfg = cfg
         self.first, self.last = first, last
+        parts = [(p, True, True) if isinstance(p, int) else tuple(p) for p in layer_ids]
         if first:
             self.tok_embeddings = Embedding(cfg.vocab_size, cfg.dim, init_std=cfg.init_std, device=device, dtype=dtype)
-        self.layers = nn.ModuleDict({str(i): LlamaBlock(cfg, device=device, dtype=dtype) for i in layer_ids})
+        self.layers = nn.ModuleDict({
+            str(i): LlamaBlock(cfg, device=device, dtype=dtype, has_attention=a, has_ffn=f) for i, a, f in parts
+        })
         if last:
             self.norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device, dtype=dtype)
             self.output = Linear(cfg.dim, cfg.vocab_size, init_std=cfg.init_std, device=device, dtype=dtype)
@@ -141,9 +229,15 @@ class LlamaStage(nn.Module):
         return h.view(B, S, -1)
 
 
-def build_llama_stage(cfg: LlamaConfig, stage: int, num_stages: int, device=None, dtype=torch.bfloat16) -> LlamaStage:
-    return LlamaStage(cfg, layer_range(cfg.n_layers, stage, num_stages), stage == 0, stage == num_stages - 1,
-                      device=device, dtype=dtype)
+def build_llama_stage(cfg: LlamaConfig, stage: int, num_stages: int, device=None, dtype=torch.bfloat16,
+                      pp_size: Optional[int] = None, seq_len: int = 4096, balance: bool = True) -> LlamaStage:
+    """Stage ``stage`` of ``num_stages``. With ``balance`` (and a known ``pp_size``) layers are assigned by
+    :func:`balanced_partition`; otherwise evenly by whole layers."""
+    if balance and pp_size is not None and num_stages > 1:
+        parts = balanced_partition(cfg, num_stages, pp_size, seq_len)[stage]
+    else:
+        parts = list(layer_range(cfg.n_layers, stage, num_stages))
+    return LlamaStage(cfg, parts, stage == 0, stage == num_stages - 1, device=device, dtype=dtype)
 
 
 class Llama(LlamaStage):

@@ -77,6 +77,7 @@ def build_llama_pipeline(
     seed: int = 0,
     record_timing: bool = False,
     schedule_kwargs: Optional[dict] = None,
+    balance: bool = True,
 ) -> Pipeline:
     """Builds this rank's Llama stages (stage ``rank + k * pp_size`` for k < virtual_stages), the schedule and
     the fused optimizer."""
@@ -93,7 +94,8 @@ def build_llama_pipeline(
     for k in range(virtual_stages):
         s = pp_rank + k * pp_size
         torch.manual_seed(seed + s)
-        module = build_llama_stage(cfg, s, num_stages, device=device, dtype=dtype)
+        module = build_llama_stage(cfg, s, num_stages, device=device, dtype=dtype, pp_size=pp_size, seq_len=seq_len,
+                                   balance=balance)
         inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
         out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1
