@@ -13,6 +13,7 @@
 // kCtaGroup == 2 pairs two CTAs of a cluster on one 256 x BN tile (tcgen05 cta_group::2): each
 // CTA loads its own 128 rows of A and its own half of B; the leader CTA issues the MMAs.
 #include "tc05.cuh"
+#include "peer.cuh"
 
 #include <string.h>
 
@@ -35,6 +36,27 @@ struct GemmParams {
   int* err;
   int num_m_tiles, num_n_tiles, num_k_blocks;
   int group_m;
+  // ---- fused tensor-parallel modes (0 = plain GEMM)
+  //   1: all-gather -> GEMM.  A is the row-wise concatenation of `world` shards of `chunk_rows` rows; this rank's
+  //      shard is read in place (tmA), the others from a local gathered copy (tmA2) that copy CTAs of this same
+  //      grid fill from the peers' shards while GEMM CTAs already work on the rows that have arrived.
+  //   2: GEMM -> reduce-scatter.  Output rows are owned chunk-wise by the ranks; tiles of a foreign chunk are stored
+  //      straight into the owner's staging slot (P2P stores), the own chunk into `C`; when everything has been
+  //      sent the grid reduces own partial + received partials into `rs_out`.
+  int fused;
+  int rank, world, chunk_rows;
+  long long lda_elems;  // row pitch (elements) of the shards and of the gathered buffer
+  int m_rot;         // rotation of the M-tile order (tiles): own chunk first (mode 1) / last (mode 2)
+  int gemm_ctas;     // CTAs running the GEMM roles; the rest of the grid copies (mode 1)
+  int epoch;
+  int* tile_flags;   // local [num_m_tiles]: rows of that M tile have landed in the gathered buffer (mode 1)
+  int* counters;     // local scratch, zeroed before launch: [0] grid barrier, [1 + peer] copy CTAs done with peer
+  int* flags[8];     // every rank's flag block (peer mapped): [0,W) ready, [W,2W) done / sent
+  const __nv_bfloat16* peer_src[8];  // mode 1: every rank's shard [chunk_rows, K] (row pitch lda)
+  __nv_bfloat16* gathered;           // mode 1: local [world * chunk_rows, K] (row pitch lda)
+  __nv_bfloat16* rs_staging[8];      // mode 2: every rank's staging [world, chunk_rows, N]
+  __nv_bfloat16* rs_out;             // mode 2: local result [chunk_rows, N] (row pitch ldc)
+  const __nv_bfloat16* rs_residual;  // mode 2: optional [chunk_rows, N] added in the final reduce
 };
 
 constexpr int BK = 64;
@@ -56,11 +78,16 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   const int r = tile - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
+  if (p.fused) {
+    tm += p.m_rot;
+    if (tm >= p.num_m_tiles) tm -= p.num_m_tiles;
+  }
 }
 
 template <int kCtaGroup, int BN, int kStages>
 __global__ void __launch_bounds__(192, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, GemmParams p) {
   constexpr int A_BYTES = BM_CTA * BK * 2;
   constexpr int BN_CTA = BN / kCtaGroup;  // B rows loaded by this CTA
   constexpr int B_BYTES = BN_CTA * BK * 2;
@@ -108,11 +135,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   const int unit = blockIdx.x / kCtaGroup;
-  const int num_units = gridDim.x / kCtaGroup;
+  const int num_units = (p.fused == 1 ? p.gemm_ctas : (int)gridDim.x) / kCtaGroup;
+  const bool copy_cta = (p.fused == 1) && ((int)blockIdx.x >= p.gemm_ctas);
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int nkb = p.num_k_blocks;
 
-  if (warp == 0) {
+  if (copy_cta) {
+    // ------------------------------------------------------------ all-gather copy role (mode 1)
+    using namespace pbp;
+    const int n_copy = (int)gridDim.x - p.gemm_ctas;
+    const int me = (int)blockIdx.x - p.gemm_ctas;
+    const int W = p.world;
+    constexpr int TILE_M = BM_CTA * kCtaGroup;
+    const int blocks_per_chunk = (p.chunk_rows + TILE_M - 1) / TILE_M;
+    const int vec_per_row = p.K / 8;
+    __shared__ int s_ok;
+    if (me == 0 && threadIdx.x < W && (int)threadIdx.x != p.rank)
+      st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);  // my shard is complete (stream order)
+    for (int q = 1; q < W; ++q) {
+      const int peer = (p.rank + q) % W;
+      if (threadIdx.x == 0) s_ok = wait_flag_sys(p.flags[p.rank] + peer, p.epoch, p.err, ERR_PEER_TIMEOUT) ? 1 : 0;
+      __syncthreads();
+      if (!s_ok) break;
+      const __nv_bfloat16* src = p.peer_src[peer];
+      for (int blk = me; blk < blocks_per_chunk; blk += n_copy) {
+        const int r0 = blk * TILE_M;
+        const int rows = min(TILE_M, p.chunk_rows - r0);
+        const long long total = (long long)rows * vec_per_row;
+        for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+          const int rr = (int)(i / vec_per_row), cc = (int)(i % vec_per_row);
+          const uint4 v = *reinterpret_cast<const uint4*>(src + (long long)(r0 + rr) * p.lda_elems + cc * 8);
+          *reinterpret_cast<uint4*>(p.gathered + ((long long)peer * p.chunk_rows + r0 + rr) * p.lda_elems + cc * 8) = v;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence();
+          st_release_gpu(p.tile_flags + (peer * p.chunk_rows + r0) / TILE_M, p.epoch);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        // the last copy CTA to finish with this peer tells it that its shard may be overwritten
+        __threadfence();
+        if (atomicAdd(p.counters + 1 + peer, 1) == n_copy - 1) st_release_sys(p.flags[peer] + W + p.rank, p.epoch);
+      }
+    }
+    if (me == 0) {
+      // do not return before every peer has finished reading my shard
+      bool ok = true;
+      if (threadIdx.x < W && (int)threadIdx.x != p.rank)
+        ok = wait_flag_sys(p.flags[p.rank] + W + threadIdx.x, p.epoch, p.err, ERR_PEER_TIMEOUT);
+      __syncthreads_and(ok);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
@@ -121,8 +196,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
         int tm, tn;
         tile_coords(tile, p, tm, tn);
-        const int m0 = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA;
+        int m0 = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA;
         const int n0 = tn * BN + cta_rank * BN_CTA;
+        const CUtensorMap* tma_a = &tmA;
+        if (p.fused == 1) {
+          const int chunk = (tm * (BM_CTA * kCtaGroup)) / p.chunk_rows;
+          if (chunk == p.rank) {
+            m0 -= chunk * p.chunk_rows;  // own shard, read in place
+          } else {
+            tma_a = &tmA2;
+            if (!pbp::wait_flag_gpu(p.tile_flags + tm, p.epoch, p.err, ERR_PEER_TIMEOUT)) {
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // copied rows -> visible to the TMA engine
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
@@ -134,10 +223,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if constexpr (kCtaGroup == 1) {
             mbar_expect_tx(&full[stage], STAGE_BYTES);
             if (!p.a_mn) {
-              tma_load_2d(a_dst, &tmA, &full[stage], k0, m0);
+              tma_load_2d(a_dst, tma_a, &full[stage], k0, m0);
             } else {
 #pragma unroll
-              for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d(a_dst + i * 8192, &tmA, &full[stage], m0 + i * 64, k0);
+              for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d(a_dst + i * 8192, tma_a, &full[stage], m0 + i * 64, k0);
             }
             if (!p.b_mn) {
               tma_load_2d(b_dst, &tmB, &full[stage], k0, n0);
@@ -149,10 +238,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (leader) mbar_expect_tx(&full[stage], STAGE_BYTES * 2);
             const uint32_t bar = full0_remote + stage * 8;
             if (!p.a_mn) {
-              tma_load_2d_pair(a_dst, &tmA, bar, k0, m0);
+              tma_load_2d_pair(a_dst, tma_a, bar, k0, m0);
             } else {
 #pragma unroll
-              for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d_pair(a_dst + i * 8192, &tmA, bar, m0 + i * 64, k0);
+              for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d_pair(a_dst + i * 8192, tma_a, bar, m0 + i * 64, k0);
             }
             if (!p.b_mn) {
               tma_load_2d_pair(b_dst, &tmB, bar, k0, n0);
@@ -220,7 +309,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t peer_ready_mask = 0;
     bool ok = true;
+    if (p.fused == 2 && blockIdx.x == 0 && warp == 2 && lane < p.world && lane != p.rank)
+      pbp::st_release_sys(p.flags[lane] + p.rank, p.epoch);  // "my previous reduce is over": peers may write to me
     const bool vec_ok = (p.ldc % 8 == 0) && (p.residual == nullptr || p.ldr % 8 == 0) &&
                         (((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.residual) |
                            reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.aux)) &
@@ -228,8 +320,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
       int tm, tn;
       tile_coords(tile, p, tm, tn);
-      const int row = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA + quarter * 32 + lane;
+      int row = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA + quarter * 32 + lane;
       const int n0 = tn * BN;
+      void* c_base = p.C;
+      int m_limit = p.M;
+      if (p.fused == 2) {
+        const int chunk = (tm * (BM_CTA * kCtaGroup)) / p.chunk_rows;
+        m_limit = (row < p.M) ? p.chunk_rows : 0;
+        row -= chunk * p.chunk_rows;
+        if (chunk != p.rank) {
+          c_base = p.rs_staging[chunk] + (long long)p.rank * p.chunk_rows * p.ldc;  // my slot in the owner's staging
+          if (!(peer_ready_mask & (1u << chunk))) {
+            // the owner must have finished reducing the previous call's partials before they are overwritten
+            bool rdy = true;
+            if (lane == 0) rdy = pbp::wait_flag_sys(p.flags[p.rank] + chunk, p.epoch, p.err, ERR_PEER_TIMEOUT);
+            rdy = __shfl_sync(0xffffffffu, rdy, 0);
+            if (!rdy) {
+              ok = false;
+              break;
+            }
+            peer_ready_mask |= 1u << chunk;
+          }
+        }
+      }
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -244,7 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
-        if (row < p.M) {
+        if (row < m_limit) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -294,7 +407,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
             if (p.out_fp32) {
-              float4* cp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0);
+              float4* cp = reinterpret_cast<float4*>(reinterpret_cast<float*>(c_base) + (long long)row * p.ldc + col0);
               if (p.accumulate) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -311,7 +424,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             } else {
               uint4* cp =
-                  reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0);
+                  reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c_base) + (long long)row * p.ldc + col0);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 o;
@@ -334,10 +447,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
               if (p.residual) x += __bfloat162float(p.residual[(long long)row * p.ldr + col]);
               if (p.out_fp32) {
-                float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+                float* cp = reinterpret_cast<float*>(c_base) + (long long)row * p.ldc + col;
                 *cp = p.accumulate ? (*cp + x) : x;
               } else {
-                reinterpret_cast<__nv_bfloat16*>(p.C)[(long long)row * p.ldc + col] = __float2bfloat16(x);
+                reinterpret_cast<__nv_bfloat16*>(c_base)[(long long)row * p.ldc + col] = __float2bfloat16(x);
               }
             }
           }
@@ -367,11 +480,72 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after_sync();
   __syncwarp();
   if (warp == 1) tmem_dealloc<kCtaGroup>(tmem_base, TMEM_COLS);
+
+  if (p.fused == 2) {
+    // ------------------------------------------------------------ reduce-scatter tail: sum what arrived
+    using namespace pbp;
+    const int W = p.world;
+    __threadfence_system();
+    if (!grid_barrier(p.counters, (int)gridDim.x, p.err, ERR_PEER_TIMEOUT)) return;
+    if (blockIdx.x == 0 && (int)threadIdx.x < W && (int)threadIdx.x != p.rank)
+      st_release_sys(p.flags[threadIdx.x] + W + p.rank, p.epoch);  // everything I owed you has been stored
+    bool ok = true;
+    if ((int)threadIdx.x < W && (int)threadIdx.x != p.rank)
+      ok = wait_flag_sys(p.flags[p.rank] + W + threadIdx.x, p.epoch, p.err, ERR_PEER_TIMEOUT);
+    if (!__syncthreads_and(ok)) return;
+    const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(p.C);
+    const __nv_bfloat16* stag = p.rs_staging[p.rank];
+    const int vec_per_row = p.N / 8;
+    const long long total = (long long)p.chunk_rows * vec_per_row;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long rr = i / vec_per_row;
+      const int cc = (int)(i % vec_per_row);
+      const long long off = rr * p.ldc + cc * 8;
+      float accv[8];
+      {
+        const uint4 u = *reinterpret_cast<const uint4*>(mine + off);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(b2[e]);
+          accv[2 * e] = f.x;
+          accv[2 * e + 1] = f.y;
+        }
+      }
+      for (int src = 0; src < W; ++src) {
+        if (src == p.rank) continue;
+        const uint4 u = *reinterpret_cast<const uint4*>(stag + (long long)src * p.chunk_rows * p.ldc + off);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(b2[e]);
+          accv[2 * e] += f.x;
+          accv[2 * e + 1] += f.y;
+        }
+      }
+      if (p.rs_residual) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p.rs_residual + off);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(b2[e]);
+          accv[2 * e] += f.x;
+          accv[2 * e + 1] += f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(accv[2 * e], accv[2 * e + 1]);
+      *reinterpret_cast<uint4*>(p.rs_out + off) = o;
+    }
+  }
 }
 
 template <int kCtaGroup, int BN, int kStages>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sm_count,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const CUtensorMap* tmA2 = nullptr, int copy_ctas = 0) {
   constexpr int A_BYTES = BM_CTA * BK * 2;
   constexpr int B_BYTES = (BN / kCtaGroup) * BK * 2;
   constexpr int SMEM = kStages * (A_BYTES + B_BYTES) + 1024 + 256;
@@ -388,11 +562,18 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.num_k_blocks = (p.K + BK - 1) / BK;
   p.group_m = kCtaGroup == 1 ? 16 : 8;
   const int tiles = p.num_m_tiles * p.num_n_tiles;
-  int units = sm_count / kCtaGroup;
+  int units = (sm_count - copy_ctas) / kCtaGroup;
   if (units > tiles) units = tiles;
+  if (units < 1) units = 1;
+  if (p.fused) {
+    const int tiles_per_chunk = p.chunk_rows / tile_m;
+    // own chunk first when gathering (its rows need no transfer), last when scattering (foreign tiles leave early)
+    p.m_rot = (p.fused == 1 ? p.rank : (p.rank + 1) % p.world) * tiles_per_chunk;
+    p.gemm_ctas = units * kCtaGroup;
+  }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(units * kCtaGroup, 1, 1);
+  cfg.gridDim = dim3(units * kCtaGroup + (p.fused == 1 ? copy_ctas : 0), 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
@@ -403,7 +584,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2 ? *tmA2 : tmA, p);
   pb_count_launch(1);
   return (int)e;
 }
@@ -475,6 +656,78 @@ int pb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
     case 3: return launch_gemm<1, 128, 6>(tmA, tmB, p, sms, stream);
     default: return -5;
   }
+}
+
+
+// Tensor-parallel fused GEMMs over peer memory (CTA-pair tiles, 256 x 256).
+//   mode 1 (all-gather -> GEMM):  C[world*chunk_rows, N] = concat_r(shard_r)[.., K] . B^T.  `a_local` is this rank's
+//       shard, `peer_src[r]` every rank's shard (peer mapped), `gathered` a local [world*chunk_rows, K] buffer.
+//   mode 2 (GEMM -> reduce-scatter): partial = A[world*chunk_rows, K] . B^T; rank r ends up with
+//       rs_out[chunk_rows, N] = sum over ranks of their partial rows [r*chunk_rows, (r+1)*chunk_rows) (+ residual).
+//       `C` is local scratch [chunk_rows, N]; `rs_staging[r]` every rank's [world, chunk_rows, N] staging buffer.
+// chunk_rows must be a multiple of 256; K, N multiples of 8; flags[r]: every rank's int[2*world] block;
+// tile_flags: local int[world*chunk_rows/256]; counters: local int[16]. All flag memory starts at zero and `epoch`
+// grows by one per call on every rank.
+int pb_gemm_tp_fused(int mode, const void* a_local, const void* B, void* C, int N, int K, long long lda,
+                     long long ldb, long long ldc, int b_mn, int rank, int world, int chunk_rows, int epoch,
+                     void** peer_src, void* gathered, void** rs_staging, void* rs_out, const void* rs_residual,
+                     int** flags, int* tile_flags, int* counters, int copy_ctas, int* err_dev, void* stream_) {
+  using namespace pb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (mode != 1 && mode != 2) return -1;
+  if (world < 2 || world > 8 || chunk_rows % 256 != 0) return -2;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || (K % 8)) return -3;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int M = world * chunk_rows;
+  CUtensorMap tmA, tmA2, tmB;
+  if (mode == 1) {
+    if (make_tmap_bf16_2d(&tmA, a_local, (uint64_t)K, (uint64_t)chunk_rows, (uint64_t)lda, 64, 128)) return -10;
+    if (make_tmap_bf16_2d(&tmA2, gathered, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128)) return -10;
+  } else {
+    if (make_tmap_bf16_2d(&tmA, a_local, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128)) return -10;
+    tmA2 = tmA;
+  }
+  int r;
+  if (!b_mn) r = make_tmap_bf16_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 128);
+  else r = make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64);
+  if (r) return -11;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.C = C;
+  p.ldc = ldc;
+  p.b_mn = b_mn;
+  p.err = err_dev;
+  p.fused = mode;
+  p.rank = rank;
+  p.world = world;
+  p.chunk_rows = chunk_rows;
+  p.lda_elems = lda;
+  p.epoch = epoch;
+  p.tile_flags = tile_flags;
+  p.counters = counters;
+  for (int i = 0; i < world; ++i) {
+    p.flags[i] = flags[i];
+    if (peer_src) p.peer_src[i] = reinterpret_cast<const __nv_bfloat16*>(peer_src[i]);
+    if (rs_staging) p.rs_staging[i] = reinterpret_cast<__nv_bfloat16*>(rs_staging[i]);
+  }
+  p.gathered = reinterpret_cast<__nv_bfloat16*>(gathered);
+  p.rs_out = reinterpret_cast<__nv_bfloat16*>(rs_out);
+  p.rs_residual = reinterpret_cast<const __nv_bfloat16*>(rs_residual);
+  cudaError_t e = cudaMemsetAsync(counters, 0, 16 * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  int sms = sm_count - g_sm_reserve;
+  if (copy_ctas < 2) copy_ctas = 2;
+  copy_ctas &= ~1;
+  // every CTA of this grid waits on others of the same grid: it must be fully resident
+  return launch_gemm<2, 256, 6>(tmA, tmB, p, sms, stream, &tmA2, mode == 1 ? copy_ctas : 0);
 }
 
 }  // extern "C"

@@ -43,6 +43,8 @@ class Pipeline:
     holds_last: bool
     losses: List[torch.Tensor] = field(default_factory=list)
 
+    tied: Any = None
+
     def train_step(self, inputs=None, target=None) -> Optional[torch.Tensor]:
         """One optimizer step over one global batch. The rank holding the first stage passes ``inputs``, the rank
         holding the last stage passes ``target`` and gets the mean loss (a device scalar) back."""
@@ -52,6 +54,8 @@ class Pipeline:
             self.schedule.step(*args, target=target, losses=self.losses)
         else:
             self.schedule.step(*args)
+        if self.tied is not None:
+            self.tied.sync_grads()
         if self.optimizer is not None:
             self.optimizer.step(grad_scale=1.0 / self.n_microbatches, zero_grad=True)
         if self.holds_last and self.losses:
@@ -78,6 +82,7 @@ def build_llama_pipeline(
     record_timing: bool = False,
     schedule_kwargs: Optional[dict] = None,
     balance: bool = True,
+    dp_group: Optional[dist.ProcessGroup] = None,
 ) -> Pipeline:
     """Builds this rank's Llama stages (stage ``rank + k * pp_size`` for k < virtual_stages), the schedule and
     the fused optimizer."""
@@ -107,6 +112,10 @@ def build_llama_pipeline(
     if with_optimizer:
         flat = FlatParams(params)
         opt = FusedAdamW(flat, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
+        if dp_group is not None and grad_reducer is None:
+            from .parallel.dp import GradReducer
+
+            grad_reducer = GradReducer(flat, dp_group)
     cls = SCHEDULES[schedule]
     kw = dict(schedule_kwargs or {})
     kw.update(loss_fn=causal_lm_loss, grad_reducer=grad_reducer, record_timing=record_timing)
@@ -118,3 +127,75 @@ def build_llama_pipeline(
         sched = cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
                     holds_last=((num_stages - 1) % pp_size == pp_rank))
+
+
+def build_gpt2_pipeline(
+    cfg,
+    global_batch: int,
+    seq_len: int,
+    n_microbatches: int,
+    device: torch.device,
+    schedule: str = "1f1b",
+    virtual_stages: int = 1,
+    group: Optional[dist.ProcessGroup] = None,
+    dp_group: Optional[dist.ProcessGroup] = None,
+    dtype: torch.dtype = torch.bfloat16,
+    lr: float = 3e-4,
+    weight_decay: float = 0.1,
+    seed: int = 0,
+    record_timing: bool = False,
+) -> Pipeline:
+    """GPT-2 stages + schedule + fused optimizer for this rank; ``global_batch`` is the batch of ONE data-parallel
+    replica. With ``dp_group`` the stage gradients are reduced by the fused NVLink all-reduce as each stage
+    finishes its backward; the tied embedding / LM head is kept in sync across the first and last pipeline rank."""
+    from .models.gpt2 import TiedEmbeddingSync, build_gpt2_stage, gpt2_loss
+
+    if dist.is_initialized():
+        pp_rank, pp_size = dist.get_rank(group), dist.get_world_size(group)
+    else:
+        pp_rank, pp_size = 0, 1
+    num_stages = pp_size * virtual_stages
+    mb = global_batch // n_microbatches
+    stages: List[ManualPipelineStage] = []
+    params = []
+    for k in range(virtual_stages):
+        s = pp_rank + k * pp_size
+        torch.manual_seed(seed + s)
+        module = build_gpt2_stage(cfg, s, num_stages, device=device, dtype=dtype)
+        inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        out = (torch.empty(mb, seq_len, cfg.padded_vocab, dtype=dtype, device="meta") if s == num_stages - 1
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        stages.append(ManualPipelineStage(module, s, num_stages, device, n_microbatches, input_args=inp,
+                                          output_args=out, group=group))
+        params.extend(module.parameters())
+    first_local = next((st for st in stages if st.is_first), None)
+    last_local = next((st for st in stages if st.is_last), None)
+    if first_local is not None and last_local is not None and first_local is not last_local:
+        # both ends of the pipeline on this rank: the head simply uses the embedding parameter
+        last_local.submod.lm_head.weight = first_local.submod.wte.weight
+    seen, unique = set(), []
+    for p_ in params:
+        if id(p_) not in seen and not any(p_ is q for q in ()):
+            seen.add(id(p_))
+            unique.append(p_)
+    params = [p_ for st in stages for p_ in st.submod.parameters()]
+    seen, unique = set(), []
+    for p_ in params:
+        if id(p_) not in seen:
+            seen.add(id(p_))
+            unique.append(p_)
+    tied = TiedEmbeddingSync(stages, group)
+    tied.broadcast()
+    flat = FlatParams(unique)
+    opt = FusedAdamW(flat, lr=lr, weight_decay=weight_decay)
+    reducer = None
+    if dp_group is not None:
+        from .parallel.dp import GradReducer
+
+        reducer = GradReducer(flat, dp_group)
+    cls = SCHEDULES[schedule]
+    kw = dict(loss_fn=gpt2_loss(cfg), grad_reducer=reducer, record_timing=record_timing)
+    sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
+    return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
+                    holds_last=((num_stages - 1) % pp_size == pp_rank), tied=tied)
