@@ -94,9 +94,79 @@ def attention_once():
     print("done")
 
 
+def bench_tp():
+    """Fused all-gather->GEMM and GEMM->reduce-scatter against NCCL + cuBLAS, Llama-2-13B layer shapes.
+    Launch with: python -m torch.distributed.run --nproc-per-node W -m pippy_b200.ops.bench_kernels tp"""
+    import os
+
+    import torch.distributed as dist
+
+    from ..parallel.tp import TPContext
+    from .gemm import set_sm_reserve
+
+    rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    W = dist.get_world_size()
+    T, d, ffn = 8192, 5120, 13824
+    rows = T // W
+    tp = TPContext(None, max_rows=rows, max_cols=max(d, 2 * ffn // W))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(10):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / 10], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    for name, n_local in (("qkv", 3 * d // W), ("gate_up", 2 * ffn // W)):
+        x = torch.randn(rows, d, device="cuda").bfloat16()
+        w = (torch.randn(n_local, d, device="cuda") * 0.02).bfloat16()
+        full = torch.empty(T, d, device="cuda", dtype=torch.bfloat16)
+
+        def baseline():
+            dist.all_gather_into_tensor(full, x)
+            return full @ w.t()
+
+        ms_f, ms_b = timed(lambda: tp.ag_gemm(x, w)), timed(baseline)
+        flops = 2 * T * n_local * d
+        wire = (W - 1) * rows * d * 2
+        roof = max(flops / 1642e12, wire / 770e9) * 1e3
+        if rank == 0:
+            print(f"all-gather->GEMM {name:8s} [{rows}->{T},{d}]x[{n_local},{d}]: fused {ms_f:.3f} ms, NCCL+cuBLAS "
+                  f"{ms_b:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_f:.2f} of roofline")
+    for name, k_local in (("o", d // W), ("down", ffn // W)):
+        x = torch.randn(T, k_local, device="cuda").bfloat16()
+        w = (torch.randn(d, k_local, device="cuda") * 0.02).bfloat16()
+        out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+
+        def baseline():
+            y = x @ w.t()
+            dist.reduce_scatter_tensor(out, y)
+            return out
+
+        ms_f, ms_b = timed(lambda: tp.gemm_rs(x, w)), timed(baseline)
+        flops = 2 * T * d * k_local
+        wire = (W - 1) * rows * d * 2
+        roof = max(flops / 1642e12, wire / 770e9) * 1e3
+        if rank == 0:
+            print(f"GEMM->reduce-scatter {name:5s} [{T},{k_local}]->[{rows},{d}]: fused {ms_f:.3f} ms, cuBLAS+NCCL "
+                  f"{ms_b:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_f:.2f} of roofline")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "attention-once": attention_once}[what]()
+    {"gemm": bench_gemm, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp}[what]()
     from . import _lib
 
     _lib.check_device_errors()
