@@ -274,3 +274,58 @@ int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared in no_alloc.h; the reference has no counterpart).
+//
+// Same math and kernels as pb_norm_bwd(layer_norm = 0), but the per-CTA partial weight gradients live in a
+// file-scope device array instead of a caller-provided buffer, so the call performs no cudaMalloc/cudaFree and
+// needs no allocator of any kind.
+namespace pbn {
+constexpr int NOALLOC_MAX_H = 8192;
+constexpr int NOALLOC_MAX_CTAS = 128;
+// [NOALLOC_MAX_CTAS][2][NOALLOC_MAX_H] floats = 8 MiB, resident on every device that loads this library
+static __device__ __align__(256) float g_noalloc_scratch[(size_t)NOALLOC_MAX_CTAS * 2 * NOALLOC_MAX_H];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace pbn
+
+extern "C" {
+
+int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_f32,
+                           int accumulate, int T, int H, void* stream_) {
+  using namespace pbn;
+  if (T <= 0 || H <= 0 || H % 8 != 0) return -1;
+  if (H > NOALLOC_MAX_H) return -2;  // beyond the built-in scratch: use pb_norm_bwd with a caller buffer instead
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -3;
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    // first call on this device: resolve the device address of the array (its name is only a host-side handle)
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int grid = NOALLOC_MAX_CTAS;
+  if (grid > T) grid = T;
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  const int nv = (H / 8 + THREADS - 1) / THREADS;
+  // every CTA overwrites its own partial row before the fold reads it, so nothing needs clearing between calls
+  if (nv <= 1) norm_bwd_kernel<false, 1><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
+  else if (nv <= 2) norm_bwd_kernel<false, 2><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
+  else norm_bwd_kernel<false, 4><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
+  norm_reduce_partials<<<(H + 255) / 256, 256, 0, stream>>>(scratch, grid, H, 0, dw_f32, nullptr, accumulate);
+  pb_count_launch(2);
+  return (int)cudaGetLastError();
+}
+
+int pb_rmsnorm_bwd_noalloc_max_hidden() { return pbn::NOALLOC_MAX_H; }
+
+}  // extern "C"
