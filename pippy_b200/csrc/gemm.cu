@@ -78,9 +78,21 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   const int r = tile - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
-  if (p.fused) {
+  if (p.fused == 1) {
     tm += p.m_rot;
     if (tm >= p.num_m_tiles) tm -= p.num_m_tiles;
+  } else if (p.fused == 2) {
+    // reduce-scatter: walk the owners round-robin, one tile group at a time, starting with the next rank, so the
+    // stores to each peer are spread over the whole kernel instead of bursting at its start
+    const int tiles_per_chunk = p.num_m_tiles / p.world;
+    if (tiles_per_chunk % p.group_m == 0) {
+      const int grp = tm / p.group_m, within = tm % p.group_m;
+      const int chunk = (p.rank + 1 + grp) % p.world;
+      tm = chunk * tiles_per_chunk + (grp / p.world) * p.group_m + within;
+    } else {
+      tm += p.m_rot;
+      if (tm >= p.num_m_tiles) tm -= p.num_m_tiles;
+    }
   }
 }
 
@@ -148,8 +160,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int W = p.world;
     constexpr int TILE_M = BM_CTA * kCtaGroup;
     const int blocks_per_chunk = (p.chunk_rows + TILE_M - 1) / TILE_M;
-    const int vec_per_row = p.K / 8;
     __shared__ int s_ok;
+    uint32_t copy_issue = 0, copy_done = 0;
     if (me == 0 && threadIdx.x < W && (int)threadIdx.x != p.rank)
       st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);  // my shard is complete (stream order)
     for (int q = 1; q < W; ++q) {
@@ -158,17 +170,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncthreads();
       if (!s_ok) break;
       const __nv_bfloat16* src = p.peer_src[peer];
-      for (int blk = me; blk < blocks_per_chunk; blk += n_copy) {
-        const int r0 = blk * TILE_M;
-        const int rows = min(TILE_M, p.chunk_rows - r0);
-        const long long total = (long long)rows * vec_per_row;
-        for (long long i = threadIdx.x; i < total; i += blockDim.x) {
-          const int rr = (int)(i / vec_per_row), cc = (int)(i % vec_per_row);
-          const uint4 v = *reinterpret_cast<const uint4*>(src + (long long)(r0 + rr) * p.lda_elems + cc * 8);
-          *reinterpret_cast<uint4*>(p.gathered + ((long long)peer * p.chunk_rows + r0 + rr) * p.lda_elems + cc * 8) = v;
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
+      // One thread streams the rows through a ring of shared-memory slots with bulk copies (peer -> smem -> local):
+      // up to kStages pieces of 32 KiB are in flight per copy CTA, enough to cover the NVLink round trip.
+      if (threadIdx.x == 0) {
+        constexpr uint32_t PIECE = 32768;
+        bool good = true;
+        for (int blk = me; blk < blocks_per_chunk && good; blk += n_copy) {
+          const int r0 = blk * TILE_M;
+          const int rows = min(TILE_M, p.chunk_rows - r0);
+          const long long bytes_total = (long long)rows * p.lda_elems * 2;
+          const char* gsrc = reinterpret_cast<const char*>(src + (long long)r0 * p.lda_elems);
+          char* gdst = reinterpret_cast<char*>(p.gathered + ((long long)peer * p.chunk_rows + r0) * p.lda_elems);
+          const int n_pieces = (int)((bytes_total + PIECE - 1) / PIECE);
+          int issued = 0, stored = 0;
+          while (stored < n_pieces) {
+            while (issued < n_pieces && issued - stored < kStages) {
+              const uint32_t slot = copy_issue % kStages;
+              const long long off = (long long)issued * PIECE;
+              const uint32_t nb = (uint32_t)min((long long)PIECE, bytes_total - off);
+              mbar_expect_tx(&full[slot], nb);
+              bulk_load(smem + slot * PIECE, gsrc + off, nb, &full[slot]);
+              ++copy_issue;
+              ++issued;
+            }
+            const uint32_t slot = copy_done % kStages;
+            if (!mbar_wait(&full[slot], (copy_done / kStages) & 1, abort_flag)) {
+              good = false;
+              atomicExch(p.err, ERR_WAIT_TIMEOUT);
+              break;
+            }
+            const long long off = (long long)stored * PIECE;
+            const uint32_t nb = (uint32_t)min((long long)PIECE, bytes_total - off);
+            bulk_store(gdst + off, smem + slot * PIECE, nb);
+            tma_store_commit();
+            tma_store_wait_read<0>();  // the slot may be refilled once the store has read it
+            ++copy_done;
+            ++stored;
+          }
+          if (!good) break;
+          tma_store_wait<0>();  // rows are in local memory
           __threadfence();
           st_release_gpu(p.tile_flags + (peer * p.chunk_rows + r0) / TILE_M, p.epoch);
         }
@@ -677,6 +717,7 @@ int pb_gemm_tp_fused(int mode, const void* a_local, const void* B, void* C, int 
   if (mode != 1 && mode != 2) return -1;
   if (world < 2 || world > 8 || chunk_rows % 256 != 0) return -2;
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || (K % 8)) return -3;
+  if (mode == 1 && lda != K) return -4;  // shards are streamed as contiguous byte ranges
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
