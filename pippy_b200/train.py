@@ -174,11 +174,6 @@ def build_gpt2_pipeline(
     if first_local is not None and last_local is not None and first_local is not last_local:
         # both ends of the pipeline on this rank: the head simply uses the embedding parameter
         last_local.submod.lm_head.weight = first_local.submod.wte.weight
-    seen, unique = set(), []
-    for p_ in params:
-        if id(p_) not in seen and not any(p_ is q for q in ()):
-            seen.add(id(p_))
-            unique.append(p_)
     params = [p_ for st in stages for p_ in st.submod.parameters()]
     seen, unique = set(), []
     for p_ in params:
@@ -199,3 +194,65 @@ def build_gpt2_pipeline(
     sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
                     holds_last=((num_stages - 1) % pp_size == pp_rank), tied=tied)
+
+
+def build_mixtral_pipeline(
+    cfg,
+    global_batch: int,
+    seq_len: int,
+    n_microbatches: int,
+    device: torch.device,
+    schedule: str = "1f1b",
+    virtual_stages: int = 1,
+    pp_group: Optional[dist.ProcessGroup] = None,
+    ep_group: Optional[dist.ProcessGroup] = None,
+    dtype: torch.dtype = torch.bfloat16,
+    lr: float = 3e-4,
+    weight_decay: float = 0.1,
+    seed: int = 0,
+    record_timing: bool = False,
+) -> Pipeline:
+    """Mixtral stages for a PP x EP layout. ``global_batch`` is the batch of ONE expert-parallel rank (EP ranks are
+    data-parallel replicas for the dense layers): dense gradients are averaged over ``ep_group`` with the fused
+    all-reduce, expert gradients stay local, token rows travel through the fused dispatch/combine kernels."""
+    from .models.mixtral import build_mixtral_stage
+    from .parallel.ep import EPContext
+
+    if dist.is_initialized():
+        pp_rank, pp_size = dist.get_rank(pp_group), dist.get_world_size(pp_group)
+        ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
+        ep_size = dist.get_world_size(ep_group) if ep_group is not None else 1
+    else:
+        pp_rank, pp_size, ep_rank, ep_size = 0, 1, 0, 1
+    num_stages = pp_size * virtual_stages
+    mb = global_batch // n_microbatches
+    ep = None
+    if ep_size > 1 and device.type == "cuda":
+        ep = EPContext(ep_group, max_tokens=mb * seq_len, hidden=cfg.dim, top_k=cfg.top_k, device=device)
+    stages: List[ManualPipelineStage] = []
+    dense, experts = [], []
+    for k in range(virtual_stages):
+        s = pp_rank + k * pp_size
+        torch.manual_seed(seed + s)  # dense parameters start identical on every expert-parallel rank
+        module = build_mixtral_stage(cfg, s, num_stages, ep, ep_size, ep_rank, device=device, dtype=dtype)
+        inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1
+               else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        stages.append(ManualPipelineStage(module, s, num_stages, device, n_microbatches, input_args=inp,
+                                          output_args=out, group=pp_group))
+        dense.extend(module.dense_parameters())
+        experts.extend(module.expert_parameters())
+    flat_dense = FlatParams(dense)
+    groups = [flat_dense] + ([FlatParams(experts)] if experts else [])
+    opt = FusedAdamW(groups, lr=lr, weight_decay=weight_decay)
+    reducer = None
+    if ep_size > 1:
+        from .parallel.dp import GradReducer
+
+        reducer = GradReducer(flat_dense, ep_group)
+    cls = SCHEDULES[schedule]
+    kw = dict(loss_fn=causal_lm_loss, grad_reducer=reducer, record_timing=record_timing)
+    sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
+    return Pipeline(stages, sched, opt, flat_dense, n_microbatches, holds_first=(pp_rank == 0),
+                    holds_last=((num_stages - 1) % pp_size == pp_rank))
