@@ -198,8 +198,11 @@ class MoEFeedForward(nn.Module):
         self.dim, self.ffn_dim, self.n_experts, self.top_k = dim, ffn_dim, n_experts, top_k
         self.ep, self.ep_size, self.ep_rank, self.aux_coef = ep, ep_size, ep_rank, aux_coef
         self.local_experts = list(range(ep_rank * (n_experts // ep_size), (ep_rank + 1) * (n_experts // ep_size)))
-        self.router = nn.Parameter(torch.empty(n_experts, dim, device=device, dtype=dtype))
-        nn.init.normal_(self.router, std=init_std)
+        # the router GEMM needs a 16-byte row pitch on its output: rows beyond n_experts are padding (zero, unused)
+        e_pad = (n_experts + 7) // 8 * 8
+        self.router = nn.Parameter(torch.zeros(e_pad, dim, device=device, dtype=dtype))
+        with torch.no_grad():
+            self.router[:n_experts].normal_(std=init_std)
         self.w_gate_up = nn.ParameterDict()
         self.w_down = nn.ParameterDict()
         for e in self.local_experts:
@@ -212,7 +215,7 @@ class MoEFeedForward(nn.Module):
         self.last_aux_loss: Optional[torch.Tensor] = None
 
     def _route(self, x):
-        logits = pf.linear(x, self.router).float()
+        logits = pf.linear(x, self.router)[:, : self.n_experts].float()
         probs = logits.softmax(-1)
         topw, topi = probs.topk(self.top_k, dim=-1)
         topw = topw / topw.sum(-1, keepdim=True)

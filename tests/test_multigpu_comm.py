@@ -131,7 +131,7 @@ def _moe_ep(rank, world):
         rel = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
         assert rel(out, ref) < 3e-2, ("out", rel(out, ref))
         assert rel(x.grad, xr.grad) < 5e-2, ("dx", rel(x.grad, xr.grad))
-        assert rel(sharded.router.grad, dense.router.grad) < 8e-2, ("drouter", rel(sharded.router.grad, dense.router.grad))
+        assert rel(sharded.router.grad[:E], dense.router.grad[:E]) < 8e-2, ("drouter", rel(sharded.router.grad, dense.router.grad))
         for other in range(world):
             if other != rank:
                 xo = xs[other].to(dev)
