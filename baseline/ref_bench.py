@@ -59,6 +59,14 @@ def main(args) -> None:
     if not os.path.isdir(os.path.join(ref_path, "pippy")):
         _unavailable("baseline/_ref/pippy is missing: the offline install of /root/reference was not done on this box")
         return
+    if int(os.environ.get("WORLD_SIZE", "1")) >= 8:
+        # Two attempts on 8 B200s completed no step: ScheduleInterleaved1F1B (killed by a 200 s timeout) and
+        # Schedule1F1B (no progress for 150 s, ended by the watchdog below); the logs are named in DESIGN.md.
+        # All of a rank's transfers share one NCCL stream there, so a send that waits for its peer blocks the
+        # receive the peer is waiting for.  The reference's GPU code is not run again at this size.
+        _unavailable("the reference's schedules (interleaved 1F1B and 1F1B) blocked inside NCCL on 8 GPUs on this "
+                     "box and completed no step; not run again (see DESIGN.md)")
+        return
     try:
         _run(args, ref_path)
     except Exception as e:  # report instead of failing the driver
@@ -104,11 +112,7 @@ def _run(args, ref_path) -> None:
     mb = args.batch // n_mb
     # one rank cannot send to itself over NCCL, so a single GPU runs one stage under 1F1B; two or more GPUs
     # run the named interleaved schedule with `virtual` stages per rank
-    # eight ranks: the reference's ScheduleInterleaved1F1B did not complete a single step in 200 s on this box
-    # (ranks blocked in its coalesced isend/irecv groups; its own comments warn that those must stay aligned
-    # "to prevent a hang"), so the reference's plain Schedule1F1B, one stage per rank, stands in there
-    interleaved_ok = world in (2, 4)
-    virtual = args.virtual if interleaved_ok else 1
+    virtual = args.virtual if world > 1 else 1
     num_stages = world * virtual
     per = n_layers // num_stages
     stages, params = [], []
@@ -130,7 +134,7 @@ def _run(args, ref_path) -> None:
 
     if virtual == 1:
         sched = Schedule1F1B(stages[0], n_mb, loss_fn=loss_fn)
-        sched_name = "1f1b (single stage)" if world == 1 else "1f1b (the reference's interleaved schedule hangs at this size)"
+        sched_name = "1f1b (single stage)"
     else:
         sched = ScheduleInterleaved1F1B(stages, n_mb, loss_fn=loss_fn)
         sched_name = "interleaved_1f1b"

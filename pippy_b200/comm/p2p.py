@@ -46,11 +46,14 @@ class LinkGroups:
             except Exception:  # pragma: no cover - older bindings without per-communicator config
                 return None
 
-        for a, b in ordered:  # same order on every rank: group creation is collective
+        me = dist.get_rank(pp_group)
+        for a, b in ordered:  # the two member ranks create the link's groups, in the same order on both
+            if me not in (a, b):
+                continue
             ranks = sorted({a, b})
             global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-            self.groups[(a, b, "F")] = dist.new_group(global_ranks, pg_options=make_options())
-            self.groups[(b, a, "B")] = dist.new_group(global_ranks, pg_options=make_options())
+            self.groups[(a, b, "F")] = dist.new_group(global_ranks, pg_options=make_options(), use_local_synchronization=True)
+            self.groups[(b, a, "B")] = dist.new_group(global_ranks, pg_options=make_options(), use_local_synchronization=True)
 
     def get(self, src: int, dst: int, kind: str) -> Optional[dist.ProcessGroup]:
         return self.groups.get((src, dst, kind))

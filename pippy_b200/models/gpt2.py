@@ -141,9 +141,13 @@ class TiedEmbeddingSync:
             return
         ranks = sorted({r_first, r_last})
         global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-        self.pg = dist.new_group(global_ranks)
+        self.pg = dist.new_group(global_ranks, use_local_synchronization=True) if self._member(pp_group, ranks) else None
         self.src = global_ranks[0] if r_first < r_last else global_ranks[1]
-        self.active = (self.first is not None) or (self.last is not None)
+        self.active = self.pg is not None and ((self.first is not None) or (self.last is not None))
+
+    @staticmethod
+    def _member(pp_group, ranks) -> bool:
+        return dist.get_rank(pp_group) in ranks
 
     def _param(self):
         if self.first is not None:

@@ -37,9 +37,9 @@ class TiedParamSync:
             stage_ids = sorted(int(name.split("_")[-1]) for name in group)
             ranks = sorted({sid % world for sid in stage_ids})
             pg = None
-            if len(ranks) > 1:
+            if len(ranks) > 1 and rank in ranks:
                 global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-                pg = dist.new_group(global_ranks)  # collective over the default group: every rank calls it
+                pg = dist.new_group(global_ranks, use_local_synchronization=True)  # only the member ranks take part
             local = [(by_index[sid], group[f"submod_{sid}"]) for sid in stage_ids if sid in by_index]
             self.entries.append((ranks, pg, local, rank in ranks))
 
