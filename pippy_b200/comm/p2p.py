@@ -14,6 +14,31 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch.distributed as dist
 
 
+def new_groups_worldwide(requests: List[List[int]], pg_options_factory=None) -> List[Optional[dist.ProcessGroup]]:
+    """Creates process groups that only some ranks need, from inside code that runs on EVERY rank of the job.
+
+    ``dist.new_group`` must be called by all ranks of the default group in the same order, members or not.  Each
+    rank passes the global-rank lists it wants (a list may repeat: the k-th repeat is a distinct group); the
+    requests are all-gathered, their union is put in one canonical order, and every rank creates every group.
+    Returns the groups for this rank's own requests, in request order."""
+    world = dist.get_world_size()
+    keyed = []
+    seen: Dict[Tuple[int, ...], int] = {}
+    for ranks in requests:
+        t = tuple(sorted(int(r) for r in ranks))
+        k = seen.get(t, 0)
+        seen[t] = k + 1
+        keyed.append((t, k))
+    gathered: List[Optional[list]] = [None] * world
+    dist.all_gather_object(gathered, keyed)
+    union = sorted({(tuple(a), int(b)) for g in gathered for a, b in g})
+    made: Dict[tuple, Optional[dist.ProcessGroup]] = {}
+    for ranks, k in union:
+        opts = pg_options_factory() if pg_options_factory is not None else None
+        made[(ranks, k)] = dist.new_group(list(ranks), pg_options=opts) if opts is not None else dist.new_group(list(ranks))
+    return [made[key] for key in keyed]
+
+
 class LinkGroups:
     """``groups[(src_group_rank, dst_group_rank, kind)]`` -> ProcessGroup, kind in {"F", "B"}."""
 
@@ -47,13 +72,17 @@ class LinkGroups:
                 return None
 
         me = dist.get_rank(pp_group)
-        for a, b in ordered:  # the two member ranks create the link's groups, in the same order on both
+        requests, keys = [], []
+        for a, b in ordered:
             if me not in (a, b):
                 continue
             ranks = sorted({a, b})
             global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-            self.groups[(a, b, "F")] = dist.new_group(global_ranks, pg_options=make_options(), use_local_synchronization=True)
-            self.groups[(b, a, "B")] = dist.new_group(global_ranks, pg_options=make_options(), use_local_synchronization=True)
+            requests += [global_ranks, global_ranks]  # one communicator per direction
+            keys += [(a, b, "F"), (b, a, "B")]
+        groups = new_groups_worldwide(requests, make_options if dist.get_backend(pp_group) == "nccl" else None)
+        for key, g in zip(keys, groups):
+            self.groups[key] = g
 
     def get(self, src: int, dst: int, kind: str) -> Optional[dist.ProcessGroup]:
         return self.groups.get((src, dst, kind))

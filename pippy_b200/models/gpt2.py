@@ -137,11 +137,15 @@ class TiedEmbeddingSync:
         world = dist.get_world_size(pp_group)
         num_stages = stages[0].num_stages
         r_first, r_last = 0, (num_stages - 1) % world
-        if r_first == r_last:
-            return
+        from ..comm.p2p import new_groups_worldwide
+
         ranks = sorted({r_first, r_last})
         global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-        self.pg = dist.new_group(global_ranks, use_local_synchronization=True) if self._member(pp_group, ranks) else None
+        member = r_first != r_last and self._member(pp_group, ranks)
+        made = new_groups_worldwide([global_ranks] if member else [])  # every rank of the job takes part
+        if r_first == r_last:
+            return
+        self.pg = made[0] if member else None
         self.src = global_ranks[0] if r_first < r_last else global_ranks[1]
         self.active = self.pg is not None and ((self.first is not None) or (self.last is not None))
 

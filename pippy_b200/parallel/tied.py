@@ -33,15 +33,20 @@ class TiedParamSync:
         world = dist.get_world_size(pp_group) if dist.is_initialized() else 1
         rank = dist.get_rank(pp_group) if dist.is_initialized() else 0
         by_index = {s.stage_index: s for s in local_stages}
+        from ..comm.p2p import new_groups_worldwide
+
+        wanted, pending = [], []
         for group in pipe.replicated_params:
             stage_ids = sorted(int(name.split("_")[-1]) for name in group)
             ranks = sorted({sid % world for sid in stage_ids})
-            pg = None
-            if len(ranks) > 1 and rank in ranks:
-                global_ranks = [dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks]
-                pg = dist.new_group(global_ranks, use_local_synchronization=True)  # only the member ranks take part
             local = [(by_index[sid], group[f"submod_{sid}"]) for sid in stage_ids if sid in by_index]
-            self.entries.append((ranks, pg, local, rank in ranks))
+            need = len(ranks) > 1 and rank in ranks
+            if need:
+                wanted.append([dist.get_global_rank(pp_group, r) if pp_group is not None else r for r in ranks])
+            pending.append((ranks, need, local))
+        made = iter(new_groups_worldwide(wanted)) if dist.is_initialized() else iter(())
+        for ranks, need, local in pending:
+            self.entries.append((ranks, next(made) if need else None, local, rank in ranks))
 
     @torch.no_grad()
     def sync(self) -> None:
