@@ -477,6 +477,7 @@ class Pipe(nn.Module):
 
         split = split_module(traced, mod, split_callback)
         split.graph.eliminate_dead_code()
+        _order_stage_calls(split)
         stage_mods = [m for n, m in split.named_children() if n.startswith("submod_") and isinstance(m, fx.GraphModule)]
         num_stages = len(stage_mods)
         for sub in stage_mods:
@@ -702,6 +703,39 @@ def _find_loss_output(g: fx.Graph, spec):
     if isinstance(out, (tuple, list)) and len(out) == 1 and not isinstance(spec, (tuple, list)):
         out = out[0]
     return _find_loss_from_output_and_spec(out, spec), output_node
+
+
+def _order_stage_calls(split: fx.GraphModule) -> None:
+    """Puts the stage calls of the split program in stage-index order, each followed by its ``getitem`` users.
+
+    ``fx.split_module`` emits parallel branches (several stages reading one producer) in an order of its own, e.g.
+    ``submod_0, submod_3, submod_2, submod_1, submod_4``.  Stage ``i`` is ``submod_i`` everywhere else (runtime
+    topology, checkpoint, schedules), so the program text is made to agree.  Values only flow from a lower to a
+    higher stage index, hence the index order is a valid topological order; ``lint`` checks it."""
+    g = split.graph
+    calls = {}
+    for n in g.nodes:
+        if n.op == "call_module" and str(n.target).startswith("submod_"):
+            calls[int(str(n.target)[len("submod_"):])] = n
+    ordered = [calls[i] for i in sorted(calls)]
+    if [n for n in g.nodes if n in set(ordered)] == ordered:
+        return
+    cursor = None
+    for n in g.nodes:
+        if n.op in ("placeholder", "get_attr"):
+            cursor = n
+    for call in ordered:
+        items = [u for u in call.users if u.op == "call_function" and u.target is operator.getitem]
+        if cursor is None:
+            next(iter(g.nodes)).prepend(call)
+        else:
+            cursor.append(call)
+        cursor = call
+        for u in items:
+            cursor.append(u)
+            cursor = u
+    g.lint()
+    split.recompile()
 
 
 def _insert_stage_symbolic_backward(split: fx.GraphModule, loss_spec) -> None:
