@@ -2,11 +2,11 @@
 //
 // One CTA owns 128 query rows of one head.  Per 128-row KV block:
 //   S = Q K^T          tcgen05.mma, both operands K-major in 128B-swizzled smem, fp32 S in TMEM
-//   softmax            one thread per query row reads its S row from TMEM (no shuffles), writes bf16 P
-//                      into swizzled smem
-//   O_j = P V          tcgen05.mma, V is the MN-major operand straight from its TMA tile
-// S is double-buffered in TMEM and P in shared memory, so S(j+1) runs during softmax(j) and P V(j) during
-// softmax(j+1).  O accumulates in TMEM across KV blocks; it is only rescaled when some row's running maximum grew
+//   softmax            one thread per query row reads its S row from TMEM (no shuffles) and writes bf16 P back
+//                      into TMEM over the first half of the same S buffer
+//   O_j = P V          tcgen05.mma with the A operand (P) in TMEM, V is the MN-major operand straight from its
+//                      TMA tile: only V crosses the shared-memory port, which is what bounds small-N MMAs
+// S/P is double-buffered in TMEM, so S(j+1) runs during softmax(j) and P V(j) during softmax(j+1).  O accumulates in TMEM across KV blocks; it is only rescaled when some row's running maximum grew
 // by more than 2^8 (the stale maximum keeps every probability <= 256, exact after the final division by l).
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (+TMEM owner), 2..9 = softmax/epilogue: two warps per TMEM lane
 // quarter, each owning 64 of the block's 128 columns (row maxima are exchanged through shared memory), so every
@@ -21,6 +21,13 @@ extern "C" void pb_count_launch(int n);
 namespace pba {
 
 using namespace pb;
+
+// one MUFU instruction; arguments here are <= 8 and very negative ones flush to zero, which is what softmax wants
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct FwdParams {
   __nv_bfloat16* o;  // [T, o_stride], head h at column h * D
@@ -42,7 +49,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr int NCH = D / 64;               // 64-column chunks per operand tile
   constexpr int CHUNK_BYTES = 128 * 128;    // 128 rows x 128 B
   constexpr int TILE_BYTES = NCH * CHUNK_BYTES;
-  constexpr int P_BYTES = 2 * CHUNK_BYTES;  // 128 x 128 bf16
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -54,8 +60,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
   uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;  // 2 buffers
-  float* s_xchg = reinterpret_cast<float*>(sP + 2 * P_BYTES);  // [2 buffers][2 halves][128 rows]
+  float* s_xchg = reinterpret_cast<float*>(sV + 2 * TILE_BYTES);  // [2 buffers][2 halves][128 rows]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_xchg + 512);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
@@ -125,23 +130,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (!ok) atomicExch(p.err, ERR_WAIT_TIMEOUT);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the loop (waits included) so that control flow stays warp-uniform; one elected lane,
+    // the same every time, issues the MMAs and their commits.
+    {
       const uint32_t idesc_s = make_idesc_bf16(128, BN, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
       bool ok = true;
       auto issue_s = [&](int j) {
         const int s = j & 1;
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * TILE_BYTES);
+        // descriptors differ only in the start address (low 14 bits, in 16-byte units): add the step offset
+        const uint64_t qd = make_smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t kd = make_smem_desc(smem_u32(sK + s * TILE_BYTES), 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-          umma_ss<1>(tS0 + s * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_s,
-                     kk != 0);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4;
+            umma_ss<1>(tS0 + s * 128, qd + off, kd + off, idesc_s, kk != 0);
+          }
+          umma_commit(&s_full[s]);
+          umma_commit(&k_empty[s]);
         }
-        umma_commit(&s_full[s]);
-        umma_commit(&k_empty[s]);
+        __syncwarp();
       };
       ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();
         issue_s(0);
@@ -150,23 +162,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (j + 1 < nblk) {
-          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag));
+          if (!ok) break;
           tc_fence_after_sync();
           issue_s(j + 1);
         }
-        if (!mbar_wait(&p_ready[s], ph, abort_flag) || !mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(&p_ready[s], ph, abort_flag) && mbar_wait(&v_full[s], ph, abort_flag));
+        if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t pa = smem_u32(sP + s * P_BYTES), va = smem_u32(sV + s * TILE_BYTES);
+        const uint64_t vd = make_smem_desc(smem_u32(sV + s * TILE_BYTES), CHUNK_BYTES, 1024);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t da = make_smem_desc(pa + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(va + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss<1>(tO, da, db, idesc_pv, (j | kk) != 0);
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            // A = P: 16 bf16 of K per step = 8 TMEM columns of the S/P buffer
+            umma_ts(tO, tS0 + s * 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, (j | kk) != 0);
+          }
+          umma_commit(&o_full[s]);
+          umma_commit(&v_empty[s]);
         }
-        umma_commit(&o_full[s]);
-        umma_commit(&v_empty[s]);
+        __syncwarp();
       }
-      if (!ok) atomicExch(p.err, ERR_WAIT_TIMEOUT);
+      if (!ok && lane == 0) atomicExch(p.err, ERR_WAIT_TIMEOUT);
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue (row x column half per thread)
@@ -177,7 +193,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     float m = -CUDART_INF_F, l = 0.f;  // l: this thread's half of the row sum
     bool ok = true;
-    const int sw = r & 7;
 
     for (int j = 0; j < nblk; ++j) {
       const int s = j & 1;
@@ -239,27 +254,22 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         l *= alpha;
         m = m_use;
       }
-      if (j >= 2) {
-        // the P buffer about to be overwritten was read by P V(j-2)
-        if (!mbar_wait(&o_full[s], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
-      }
-      uint8_t* p_row = sP + s * P_BYTES + half * CHUNK_BYTES + r * 128;
+      // P goes back into TMEM over columns [0, 64) of this S buffer (2 bf16 per 32-bit column).  Both warps of a
+      // lane quarter have their S values in registers since before the exchange barrier above, and P V(j-2), the
+      // last reader of this buffer, completed before S(j) (the tensor pipe runs its MMAs in issue order).
       float rowsum = 0.f;
+      uint32_t pk[32];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        uint4 w;
-        __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float x0 = exp2f(__uint_as_float(v[u >> 2][(u & 3) * 8 + e * 2]) * p.scale_log2 - m);
-          const float x1 = exp2f(__uint_as_float(v[u >> 2][(u & 3) * 8 + e * 2 + 1]) * p.scale_log2 - m);
-          rowsum += x0 + x1;
-          wb[e] = __floats2bfloat162_rn(x0, x1);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((u ^ sw) * 16)) = w;
+      for (int e = 0; e < 32; ++e) {
+        const float x0 = fast_exp2(__uint_as_float(v[e >> 4][(e & 15) * 2]) * p.scale_log2 - m);
+        const float x1 = fast_exp2(__uint_as_float(v[e >> 4][(e & 15) * 2 + 1]) * p.scale_log2 - m);
+        rowsum += x0 + x1;
+        __nv_bfloat162 w = __floats2bfloat162_rn(x0, x1);
+        pk[e] = *reinterpret_cast<uint32_t*>(&w);
       }
+      tmem_st_32x32(tS0 + s * 128 + lane_off + half * 32, pk);
+      tmem_st_wait();
       l += rowsum;
-      fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&p_ready[s]);
     }
@@ -314,7 +324,7 @@ template <int D>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                       cudaStream_t stream) {
   constexpr int TILE = (D / 64) * 128 * 128;
-  constexpr int SMEM = 5 * TILE + 2 * (2 * 128 * 128) + 2048 + 256;
+  constexpr int SMEM = 5 * TILE + 2048 + 256;
   auto kern = fa_fwd_kernel<D>;
   static bool attr_set = false;
   if (!attr_set) {
