@@ -28,6 +28,11 @@ namespace pbb {
 
 using namespace pb;
 
+template <bool V>
+struct MaskTag {
+  static constexpr bool value = V;
+};
+
 // one MUFU instruction; the argument is log2 of a probability (<= 0 up to rounding), very negative ones flush to 0
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -345,48 +350,54 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
       // to the accumulated dQ / dK in the epilogue), write the bf16 pairs back over the same columns.  A small live
       // set leaves the scheduler room to overlap the exponentials of one element with the arithmetic of others.
       const uint32_t ta = s * 64 + lane_off + half * 32;
+      // The masked variant (diagonal and ragged blocks only) is a separate instantiation: a per-element test of a
+      // run-time flag costs a branch per element, which serialises the otherwise independent elements.
+      auto do_block = [&](auto masked) {
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t t1[16], t2[16];
-        tmem_ld_32x16(tT1 + ta + ch * 16, t1);
-        tmem_ld_32x16(tT2 + ta + ch * 16, t2);
-        tmem_ld_wait();
-        uint32_t pk_p[8], pk_ds[8];  // 16 bf16 each
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t t1[16], t2[16];
+          tmem_ld_32x16(tT1 + ta + ch * 16, t1);
+          tmem_ld_32x16(tT2 + ta + ch * 16, t2);
+          tmem_ld_wait();
+          uint32_t pk_p[8], pk_ds[8];  // 16 bf16 each
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          float lse2[2], dl2[2];
-          if (kMode == 0) {
-            const float2 a = *reinterpret_cast<const float2*>(&lse_buf[half * 32 + ch * 16 + e]);
-            const float2 d2 = *reinterpret_cast<const float2*>(&dl_buf[half * 32 + ch * 16 + e]);
-            lse2[0] = a.x; lse2[1] = a.y;
-            dl2[0] = d2.x; dl2[1] = d2.y;
-          } else {
-            lse2[0] = lse2[1] = my_lse2;
-            dl2[0] = dl2[1] = my_delta;
-          }
-          float pv[2], dv[2];
-#pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            float pr = fast_exp2(__uint_as_float(t1[e + w]) * p.scale_log2 - lse2[w]);
-            if (need_mask) {
-              const int str_idx = c0 + half * 32 + ch * 16 + e + w;
-              const int qi = (kMode == 0) ? str_idx : res_idx;
-              const int ki = (kMode == 0) ? res_idx : str_idx;
-              const bool valid = (qi < p.S) && (ki < p.S) && (!p.causal || ki <= qi);
-              pr = valid ? pr : 0.f;
+          for (int e = 0; e < 16; e += 2) {
+            float lse2[2], dl2[2];
+            if (kMode == 0) {
+              const float2 a = *reinterpret_cast<const float2*>(&lse_buf[half * 32 + ch * 16 + e]);
+              const float2 d2 = *reinterpret_cast<const float2*>(&dl_buf[half * 32 + ch * 16 + e]);
+              lse2[0] = a.x; lse2[1] = a.y;
+              dl2[0] = d2.x; dl2[1] = d2.y;
+            } else {
+              lse2[0] = lse2[1] = my_lse2;
+              dl2[0] = dl2[1] = my_delta;
             }
-            pv[w] = pr;
-            dv[w] = pr * (__uint_as_float(t2[e + w]) - dl2[w]);
+            float pv[2], dv[2];
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+              float pr = fast_exp2(__uint_as_float(t1[e + w]) * p.scale_log2 - lse2[w]);
+              if constexpr (decltype(masked)::value) {
+                const int str_idx = c0 + half * 32 + ch * 16 + e + w;
+                const int qi = (kMode == 0) ? str_idx : res_idx;
+                const int ki = (kMode == 0) ? res_idx : str_idx;
+                const bool valid = (qi < p.S) && (ki < p.S) && (!p.causal || ki <= qi);
+                pr = valid ? pr : 0.f;
+              }
+              pv[w] = pr;
+              dv[w] = pr * (__uint_as_float(t2[e + w]) - dl2[w]);
+            }
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(pv[0], pv[1]);
+            __nv_bfloat162 d0 = __floats2bfloat162_rn(dv[0], dv[1]);
+            pk_p[e / 2] = *reinterpret_cast<uint32_t*>(&a0);
+            pk_ds[e / 2] = *reinterpret_cast<uint32_t*>(&d0);
           }
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(pv[0], pv[1]);
-          __nv_bfloat162 d0 = __floats2bfloat162_rn(dv[0], dv[1]);
-          pk_p[e / 2] = *reinterpret_cast<uint32_t*>(&a0);
-          pk_ds[e / 2] = *reinterpret_cast<uint32_t*>(&d0);
+          // back into TMEM over this thread's own score columns: 16 values = 8 columns at half * 32 + ch * 8
+          if (kMode == 0) tmem_st_32x8(tT1 + ta + ch * 8, pk_p);
+          tmem_st_32x8((kMode == 0 ? tT2 : tT1) + ta + ch * 8, pk_ds);
         }
-        // back into TMEM over this thread's own score columns: 16 values = 8 columns at half * 32 + ch * 8
-        if (kMode == 0) tmem_st_32x8(tT1 + ta + ch * 8, pk_p);
-        tmem_st_32x8((kMode == 0 ? tT2 : tT1) + ta + ch * 8, pk_ds);
-      }
+      };
+      if (need_mask) do_block(MaskTag<true>{});
+      else do_block(MaskTag<false>{});
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&ds_ready[s]);
