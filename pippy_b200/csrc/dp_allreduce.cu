@@ -23,6 +23,7 @@ using namespace pbp;
 
 constexpr int MAX_RANKS = 8;
 constexpr int THREADS = 512;
+constexpr int UNROLL = 4;  // independent 8-element groups per thread and loop trip: the passes are latency-bound otherwise
 
 struct Params {
   float* grad;                        // local fp32 gradients [n]
@@ -63,12 +64,24 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
   int bar = p.barrier_base;
 
   // ---- phase 0: cast + scale into the wire buffer
-  for (long long i = tid; i < nvec; i += nthreads) {
-    const float4 a = reinterpret_cast<const float4*>(p.grad)[2 * i];
-    const float4 b = reinterpret_cast<const float4*>(p.grad)[2 * i + 1];
-    float f[8] = {a.x * p.scale, a.y * p.scale, a.z * p.scale, a.w * p.scale,
-                  b.x * p.scale, b.y * p.scale, b.z * p.scale, b.w * p.scale};
-    reinterpret_cast<uint4*>(my_stage)[i] = pack8(f);
+  for (long long i0 = tid; i0 < nvec; i0 += nthreads * UNROLL) {
+    float4 a[UNROLL], b[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < nvec) {
+        a[u] = reinterpret_cast<const float4*>(p.grad)[2 * i];
+        b[u] = reinterpret_cast<const float4*>(p.grad)[2 * i + 1];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i >= nvec) continue;
+      float f[8] = {a[u].x * p.scale, a[u].y * p.scale, a[u].z * p.scale, a[u].w * p.scale,
+                    b[u].x * p.scale, b[u].y * p.scale, b[u].z * p.scale, b[u].w * p.scale};
+      reinterpret_cast<uint4*>(my_stage)[i] = pack8(f);
+    }
   }
   __threadfence_system();
   bar += gridDim.x;
@@ -82,24 +95,52 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
   const long long per = (nvec + W - 1) / W;
   const long long lo = per * p.rank;
   const long long hi = (lo + per < nvec) ? lo + per : nvec;
-  for (long long i = lo + tid; i < hi; i += nthreads) {
-    const float4 a = reinterpret_cast<const float4*>(p.grad)[2 * i];
-    const float4 b = reinterpret_cast<const float4*>(p.grad)[2 * i + 1];
-    float acc[8] = {a.x * p.scale, a.y * p.scale, a.z * p.scale, a.w * p.scale,
-                    b.x * p.scale, b.y * p.scale, b.z * p.scale, b.w * p.scale};
-    for (int q = 1; q < W; ++q) {
-      const int peer = (p.rank + q) % W;
-      float f[8];
-      unpack8(reinterpret_cast<const uint4*>(p.staging[peer])[i], f);
+  for (long long i0 = lo + tid; i0 < hi; i0 += nthreads * UNROLL) {
+    float acc[UNROLL][8];
+    // own fp32 values and, peer by peer, UNROLL remote vectors in flight at once (a peer load takes microseconds)
+    {
+      float4 a[UNROLL], b[UNROLL];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < hi) {
+          a[u] = reinterpret_cast<const float4*>(p.grad)[2 * i];
+          b[u] = reinterpret_cast<const float4*>(p.grad)[2 * i + 1];
+        } else {
+          a[u] = b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        acc[u][0] = a[u].x * p.scale; acc[u][1] = a[u].y * p.scale; acc[u][2] = a[u].z * p.scale;
+        acc[u][3] = a[u].w * p.scale; acc[u][4] = b[u].x * p.scale; acc[u][5] = b[u].y * p.scale;
+        acc[u][6] = b[u].z * p.scale; acc[u][7] = b[u].w * p.scale;
+      }
     }
-    reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    const uint4 packed = pack8(acc);
     for (int q = 1; q < W; ++q) {
-      const int peer = (p.rank + q) % W;
-      reinterpret_cast<uint4*>(p.staging[peer])[i] = packed;
+      const uint4* src = reinterpret_cast<const uint4*>(p.staging[(p.rank + q) % W]);
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * nthreads;
+        v[u] = (i < hi) ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] += f[j];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i >= hi) continue;
+      reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+      reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+      const uint4 packed = pack8(acc[u]);
+      for (int q = 1; q < W; ++q) reinterpret_cast<uint4*>(p.staging[(p.rank + q) % W])[i] = packed;
     }
   }
   __threadfence_system();
@@ -111,12 +152,22 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
   if (!__syncthreads_and(ok)) return;
 
   // ---- phase 2: slices owned by the others are now complete in my staging buffer
-  for (long long i = tid; i < nvec; i += nthreads) {
-    if (i >= lo && i < hi) continue;
-    float f[8];
-    unpack8(reinterpret_cast<const uint4*>(my_stage)[i], f);
-    reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
-    reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
+  for (long long i0 = tid; i0 < nvec; i0 += nthreads * UNROLL) {
+    uint4 v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < nvec && !(i >= lo && i < hi)) v[u] = reinterpret_cast<const uint4*>(my_stage)[i];
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i >= nvec || (i >= lo && i < hi)) continue;
+      float f[8];
+      unpack8(v[u], f);
+      reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
+      reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
   }
 }
 

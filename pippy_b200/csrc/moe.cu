@@ -21,6 +21,8 @@ namespace pbmoe {
 using namespace pbp;
 constexpr int MAX_RANKS = 8;
 constexpr int THREADS = 256;
+constexpr int UNROLL = 4;   // 16-byte vectors a lane keeps in flight per source row
+constexpr int MAX_TOPK = 4;
 
 struct Comm {
   int* flags[MAX_RANKS];  // every rank's flag block: [0,W) phase A, [W,2W) phase B
@@ -69,17 +71,25 @@ __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat
     const uint4* src = reinterpret_cast<const uint4*>(x + (a / k) * H);
     uint4* dst = reinterpret_cast<uint4*>(s_recv[d] + row * H);
     const float s = scale ? scale[a] : 1.f;
-    for (int v = lane; v < vec; v += 32) {
-      uint4 u = src[v];
-      if (scale) {
-        __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+    // four independent 16-byte loads per lane before the first store: the copy is latency-bound otherwise
+    for (int v0 = lane; v0 < vec; v0 += 32 * UNROLL) {
+      uint4 u[UNROLL];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __bfloat1622float2(b[j]);
-          b[j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      for (int i = 0; i < UNROLL; ++i)
+        if (v0 + i * 32 < vec) u[i] = __ldg(src + v0 + i * 32);
+#pragma unroll
+      for (int i = 0; i < UNROLL; ++i) {
+        if (v0 + i * 32 >= vec) continue;
+        if (scale) {
+          __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u[i]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(b[j]);
+            b[j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+          }
         }
+        dst[v0 + i * 32] = u[i];
       }
-      dst[v] = u;
     }
   }
   __threadfence_system();
@@ -104,28 +114,48 @@ __global__ void __launch_bounds__(THREADS) moe_combine_kernel(__nv_bfloat16* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vec = H / 8;
   for (long long t = blockIdx.x * warps_per_block + warp; t < T; t += (long long)gridDim.x * warps_per_block) {
-    for (int v0 = lane; v0 < vec; v0 += 32) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j = 0; j < k; ++j) {
+    // the k source rows of this token: looked up once, not once per vector
+    const uint4* rows[MAX_TOPK];
+    float w[MAX_TOPK];
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j) {
+      if (j < k) {
         const long long a = t * k + j;
         const int e = expert[a];
-        const long long row = (long long)dst_base[e] + slot[a];
-        const uint4 u = reinterpret_cast<const uint4*>(s_y[e / experts_per_rank] + row * H)[v0];
-        if (save) reinterpret_cast<uint4*>(save + a * H)[v0] = u;
-        const float w = weight ? weight[a] : 1.f;
-        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(b[q]);
-          acc[2 * q] += w * f.x;
-          acc[2 * q + 1] += w * f.y;
-        }
+        rows[j] = reinterpret_cast<const uint4*>(s_y[e / experts_per_rank] + ((long long)dst_base[e] + slot[a]) * H);
+        w[j] = weight ? weight[a] : 1.f;
       }
-      uint4 o;
-      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+    }
+    // peer loads take microseconds: every lane issues k * UNROLL of them before it touches the first result
+    for (int v0 = lane; v0 < vec; v0 += 32 * UNROLL) {
+      uint4 u[MAX_TOPK][UNROLL];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) ob[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-      reinterpret_cast<uint4*>(out + t * H)[v0] = o;
+      for (int j = 0; j < MAX_TOPK; ++j)
+#pragma unroll
+        for (int i = 0; i < UNROLL; ++i)
+          if (j < k && v0 + i * 32 < vec) u[j][i] = rows[j][v0 + i * 32];
+#pragma unroll
+      for (int i = 0; i < UNROLL; ++i) {
+        if (v0 + i * 32 >= vec) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) {
+          if (j >= k) continue;
+          if (save) reinterpret_cast<uint4*>(save + (t * k + j) * H)[v0 + i * 32] = u[j][i];
+          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u[j][i]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(b[q]);
+            acc[2 * q] += w[j] * f.x;
+            acc[2 * q + 1] += w[j] * f.y;
+          }
+        }
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ob[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+        reinterpret_cast<uint4*>(out + t * H)[v0 + i * 32] = o;
+      }
     }
   }
   if (!grid_barrier(c.counter, (int)gridDim.x, c.err, 3)) return;
@@ -200,7 +230,7 @@ int pb_moe_combine(void* out, const int* expert, const int* slot, const int* dst
                    void* y_ptrs_dev, void* save, int T, int k, int H, int experts_per_rank, int** flags,
                    int* counter, int* err, int rank, int world, int epoch, int ctas, void* stream_) {
   using namespace pbmoe;
-  if (H % 8 != 0 || world > MAX_RANKS) return -1;
+  if (H % 8 != 0 || world > MAX_RANKS || k > MAX_TOPK) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;

@@ -3,6 +3,7 @@
     python -m pippy_b200.ops.bench_kernels gemm
     python -m pippy_b200.ops.bench_kernels attention
     python -m pippy_b200.ops.bench_kernels attention-once     # two forward+backward calls on a small case, for ncu
+    python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe
 
 Library rates (cuBLAS via torch.matmul, SDPA) are printed beside ours for scale.
 """
@@ -164,9 +165,145 @@ def bench_tp():
     dist.destroy_process_group()
 
 
+def _dist_setup():
+    import os
+
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    return rank, dist.get_world_size()
+
+
+def _dist_timed(fn, iters=10):
+    import torch.distributed as dist
+
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def bench_dp():
+    """Fused cast + scale + all-reduce of a stage's fp32 gradient buffer (bf16 on the wire) against NCCL.
+    Launch with: python -m torch.distributed.run --nproc-per-node W -m pippy_b200.ops.bench_kernels dp"""
+    import torch.distributed as dist
+
+    from ..optim import FlatParams
+    from ..parallel.dp import GradReducer
+
+    rank, W = _dist_setup()
+    for n in (21_000_000, 60_700_000, 256 * 1024 * 1024):  # GPT-2 stages (small / with embeddings), a 1 GiB buffer
+        n = n // 64 * 64
+        flat = FlatParams([torch.nn.Parameter(torch.zeros(n, device="cuda", dtype=torch.bfloat16))])
+        flat.grad.normal_()
+        red = GradReducer(flat, None)
+
+        def fused():
+            red.reduce_all()
+            red.finish()
+
+        wire16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+
+        def nccl_bf16():
+            torch.mul(flat.grad, 1.0 / W, out=flat.grad)
+            wire16.copy_(flat.grad)
+            dist.all_reduce(wire16)
+            flat.grad.copy_(wire16)
+
+        def nccl_fp32():
+            flat.grad.mul_(1.0 / W)
+            dist.all_reduce(flat.grad)
+
+        ms_f, ms_16, ms_32 = _dist_timed(fused), _dist_timed(nccl_bf16), _dist_timed(nccl_fp32)
+        # two-shot all-reduce: every rank sends and receives (W - 1) / W of the bf16 buffer twice
+        wire = 2 * (W - 1) / W * n * 2
+        roof = max(wire / 770e9, (n * 4 * 2) / 6549e9) * 1e3  # NVLink vs reading + writing the fp32 buffer in HBM
+        if rank == 0:
+            print(f"DP all-reduce {n / 1e6:7.1f} M grads, {W} ranks: fused {ms_f:.3f} ms, NCCL bf16 wire (scale, cast, "
+                  f"all-reduce, cast back) {ms_16:.3f} ms, NCCL fp32 {ms_32:.3f} ms, roofline {roof:.3f} ms -> "
+                  f"{roof / ms_f:.2f} of roofline")
+        del red, flat
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def bench_moe():
+    """Fused permute + all-to-all dispatch and combine + weighted sum against all_to_all_single + index ops.
+    Launch with: python -m torch.distributed.run --nproc-per-node W -m pippy_b200.ops.bench_kernels moe"""
+    import torch.distributed as dist
+
+    from ..parallel.ep import EPContext, _Plan
+
+    rank, W = _dist_setup()
+    T, H, E, K = 8192, 4096, 8, 2
+    ep = EPContext(None, max_tokens=T, hidden=H, top_k=K)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    wgt, idx = torch.softmax(logits, -1).topk(K, dim=-1)
+    expert = idx.to(torch.int32).reshape(-1).contiguous()
+    weight = (wgt / wgt.sum(-1, keepdim=True)).float().reshape(-1).contiguous()
+    plan = _Plan(ep, expert, E)
+    out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    save = torch.empty(T * K, H, device="cuda", dtype=torch.bfloat16)
+    epr = E // W
+
+    def fused_dispatch():
+        ep.dispatch(x, expert, plan.slot, plan.dst_base, None, epr)
+
+    def fused_combine():
+        ep.combine(out, expert, plan.slot, plan.dst_base, weight, save, epr)
+
+    # the library way: sort assignments by destination expert, exchange counts-sized slabs, un-sort and weight
+    order = torch.argsort(expert.long(), stable=True)
+    tok = (order // K)
+    counts = torch.bincount(expert.long(), minlength=E)
+    send_splits = counts.view(W, epr).sum(1).tolist()
+    allc = torch.empty(W, E, dtype=torch.int64, device="cuda")
+    dist.all_gather_into_tensor(allc, counts)
+    recv_splits = allc[:, rank * epr:(rank + 1) * epr].sum(1).tolist()
+    recv_buf = torch.empty(sum(recv_splits), H, device="cuda", dtype=torch.bfloat16)
+    back = torch.empty(T * K, H, device="cuda", dtype=torch.bfloat16)
+
+    def lib_dispatch():
+        dist.all_to_all_single(recv_buf, x[tok], recv_splits, send_splits)
+
+    def lib_combine():
+        dist.all_to_all_single(back, recv_buf, send_splits, recv_splits)
+        contrib = back.float() * weight[order].unsqueeze(1)
+        o = torch.zeros(T, H, device="cuda", dtype=torch.float32)
+        o.index_add_(0, tok, contrib)
+        return o.bfloat16()
+
+    ms_fd, ms_ld = _dist_timed(fused_dispatch), _dist_timed(lib_dispatch)
+    ms_fc, ms_lc = _dist_timed(fused_combine), _dist_timed(lib_combine)
+    rows_remote = T * K * (W - 1) / W  # expected rows that leave this rank
+    wire = rows_remote * H * 2
+    roof = max(wire / 770e9, (T * K * H * 2 * 2) / 6549e9) * 1e3
+    if rank == 0:
+        print(f"MoE dispatch T{T} top-{K} H{H} E{E}, {W} ranks: fused {ms_fd:.3f} ms, all_to_all_single + gather "
+              f"{ms_ld:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_fd:.2f} of roofline")
+        print(f"MoE combine  T{T} top-{K} H{H} E{E}, {W} ranks: fused {ms_fc:.3f} ms, all_to_all_single + index_add "
+              f"{ms_lc:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_fc:.2f} of roofline")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp}[what]()
+    {"gemm": bench_gemm, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
+     "dp": bench_dp, "moe": bench_moe}[what]()
     from . import _lib
 
     _lib.check_device_errors()

@@ -23,7 +23,7 @@ from ..optim import FlatParams
 
 
 class GradReducer:
-    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 32,
+    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 64,
                  average: bool = True):
         self.flat = flat
         self.group = dp_group

@@ -32,7 +32,7 @@ class EPContext:
     """Peer-mapped workspaces of one expert-parallel group, shared by all MoE layers (calls are stream ordered)."""
 
     def __init__(self, group: Optional[dist.ProcessGroup], max_tokens: int, hidden: int, top_k: int = 2, device=None,
-                 ctas: int = 48):
+                 ctas: int = 96):
         from ..comm.symm import SymmetricBuffer
 
         self.group = group
