@@ -117,6 +117,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = bars + 2 * kStages + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* sEpi = smem + kStages * STAGE_BYTES + 256;  // 4 epilogue warps x 32 rows x (128 + 16) bytes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -364,12 +365,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = tn * BN;
       void* c_base = p.C;
       int m_limit = p.M;
+      bool peer_tile = false;
       if (p.fused == 2) {
         const int chunk = (tm * (BM_CTA * kCtaGroup)) / p.chunk_rows;
         m_limit = (row < p.M) ? p.chunk_rows : 0;
         row -= chunk * p.chunk_rows;
         if (chunk != p.rank) {
           c_base = p.rs_staging[chunk] + (long long)p.rank * p.chunk_rows * p.ldc;  // my slot in the owner's staging
+          // Tiles that leave over NVLink go out as whole 128-byte row pieces: a lane owns a row, so its direct
+          // stores are 16-byte pieces 32 rows apart, which use a fraction of the link; two 32-column chunks are
+          // staged in shared memory and written back with 8 lanes per row instead.
+          peer_tile = vec_ok && !p.out_fp32 && (n0 + BN <= p.N) && (p.M % 32 == 0) && p.bias == nullptr &&
+                      p.act == 0 && p.residual == nullptr;
           if (!(peer_ready_mask & (1u << chunk))) {
             // the owner must have finished reducing the previous call's partials before they are overwritten
             bool rdy = true;
@@ -464,7 +471,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             } else {
               uint4* cp =
-                  reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c_base) + (long long)row * p.ldc + col0);
+                  peer_tile
+                      ? reinterpret_cast<uint4*>(sEpi + ((warp - 2) * 32 + lane) * 144 + (c & 1) * 64)
+                      : reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c_base) + (long long)row * p.ldc +
+                                                 col0);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 o;
@@ -494,6 +504,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           }
+        }
+        if (peer_tile && (c & 1)) {
+          // 32 rows x 128 bytes staged by this warp: piece i = q * 32 + lane is bytes [16 * (i % 8), +16) of row i / 8
+          __syncwarp();
+          const int row_w = row - lane;  // first row of this warp's block, relative to the owner's chunk
+          const uint8_t* stage = sEpi + (warp - 2) * 32 * 144;
+          __nv_bfloat16* dst0 = reinterpret_cast<__nv_bfloat16*>(c_base) + n0 + (c - 1) * 32;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int i = q * 32 + lane;
+            const int rr = i >> 3, part = i & 7;
+            if (row_w + rr < m_limit && row_w + rr >= 0) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + rr * 144 + part * 16);
+              *reinterpret_cast<uint4*>(dst0 + (long long)(row_w + rr) * p.ldc + part * 8) = val;
+            }
+          }
+          __syncwarp();
         }
       }
       tc_fence_before_sync();
@@ -537,48 +564,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const __nv_bfloat16* stag = p.rs_staging[p.rank];
     const int vec_per_row = p.N / 8;
     const long long total = (long long)p.chunk_rows * vec_per_row;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-      const long long rr = i / vec_per_row;
-      const int cc = (int)(i % vec_per_row);
-      const long long off = rr * p.ldc + cc * 8;
-      float accv[8];
-      {
-        const uint4 u = *reinterpret_cast<const uint4*>(mine + off);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    // Four output vectors per thread and trip, all their loads issued before the first use: with one vector in
+    // flight per thread this pass ran at a fraction of the HBM rate.
+    constexpr int RU = 4;
+    const long long nthr = (long long)gridDim.x * blockDim.x;
+    auto add8 = [](float* accv, const uint4& u) {
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(b2[e]);
-          accv[2 * e] = f.x;
-          accv[2 * e + 1] = f.y;
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(b2[e]);
+        accv[2 * e] += f.x;
+        accv[2 * e + 1] += f.y;
+      }
+    };
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += nthr * RU) {
+      long long off[RU];
+      uint4 own[RU], res[RU];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const long long i = i0 + u * nthr;
+        off[u] = -1;
+        if (i < total) {
+          off[u] = (i / vec_per_row) * p.ldc + (i % vec_per_row) * 8;
+          own[u] = *reinterpret_cast<const uint4*>(mine + off[u]);
+          if (p.rs_residual) res[u] = *reinterpret_cast<const uint4*>(p.rs_residual + off[u]);
+        }
+      }
+      float accv[RU][8];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) accv[u][e] = 0.f;
+        if (off[u] >= 0) {
+          add8(accv[u], own[u]);
+          if (p.rs_residual) add8(accv[u], res[u]);
         }
       }
       for (int src = 0; src < W; ++src) {
         if (src == p.rank) continue;
-        const uint4 u = *reinterpret_cast<const uint4*>(stag + (long long)src * p.chunk_rows * p.ldc + off);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const __nv_bfloat16* base = stag + (long long)src * p.chunk_rows * p.ldc;
+        uint4 v[RU];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(b2[e]);
-          accv[2 * e] += f.x;
-          accv[2 * e + 1] += f.y;
-        }
+        for (int u = 0; u < RU; ++u)
+          if (off[u] >= 0) v[u] = *reinterpret_cast<const uint4*>(base + off[u]);
+#pragma unroll
+        for (int u = 0; u < RU; ++u)
+          if (off[u] >= 0) add8(accv[u], v[u]);
       }
-      if (p.rs_residual) {
-        const uint4 u = *reinterpret_cast<const uint4*>(p.rs_residual + off);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(b2[e]);
-          accv[2 * e] += f.x;
-          accv[2 * e + 1] += f.y;
-        }
+      for (int u = 0; u < RU; ++u) {
+        if (off[u] < 0) continue;
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(accv[u][2 * e], accv[u][2 * e + 1]);
+        *reinterpret_cast<uint4*>(p.rs_out + off[u]) = o;
       }
-      uint4 o;
-      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(accv[2 * e], accv[2 * e + 1]);
-      *reinterpret_cast<uint4*>(p.rs_out + off) = o;
     }
   }
 }
@@ -588,7 +629,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
                        cudaStream_t stream, const CUtensorMap* tmA2 = nullptr, int copy_ctas = 0) {
   constexpr int A_BYTES = BM_CTA * BK * 2;
   constexpr int B_BYTES = (BN / kCtaGroup) * BK * 2;
-  constexpr int SMEM = kStages * (A_BYTES + B_BYTES) + 1024 + 256;
+  constexpr int SMEM = kStages * (A_BYTES + B_BYTES) + 1024 + 256 + 4 * 32 * 144;
   auto kern = gemm_bf16_kernel<kCtaGroup, BN, kStages>;
   static bool attr_set = false;
   if (!attr_set) {
