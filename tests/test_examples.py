@@ -31,6 +31,7 @@ def _run(path, nproc, *args, timeout=600):
     ("cpu_init/cpu_init.py", 2),
     ("checkpoint/toy_checkpoint.py", 2),
     ("profiling/mlp_profiling.py", 2),
+    ("huggingface/pippy_unet.py", 2),
 ])
 def test_example_runs(path, nproc, tmp_path):
     _run(path, nproc)
