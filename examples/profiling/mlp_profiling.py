@@ -32,5 +32,9 @@ if __name__ == "__main__":
     prof.export_chrome_trace(os.path.join(out, f"pipeline_rank{rank}.json"))
     stats = schedule.last_step_stats
     print(f"rank {rank}: bubble {stats['bubble']:.3f}, per-op seconds {stats['per_op_s']}")
+    # every rank's measured actions of the last step on one time axis (open in chrome://tracing or Perfetto)
+    from pippy_b200.schedules import gather_measured_trace
+
+    gather_measured_trace(schedule, os.path.join(out, "pipeline_schedule.json"))
     dist.barrier()
     dist.destroy_process_group()

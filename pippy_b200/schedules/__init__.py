@@ -14,3 +14,4 @@ from .runtime import (
     sorted_batch_isend_irecv,
 )
 from .simulator import SimResult, ideal_bubble, simulate
+from .trace import gather_measured_trace, measured_trace, simulated_trace, write_chrome_trace

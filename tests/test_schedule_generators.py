@@ -122,3 +122,27 @@ def test_reduce_grad_placed_after_last_weight_action():
         idx = [i for i, a in enumerate(acts) if a.op == Op.REDUCE_GRAD]
         assert len(idx) == 1
         assert all(a.op not in (Op.W, Op.B) for a in acts[idx[0] + 1:])
+
+
+def test_chrome_trace_of_simulated_and_measured_timelines(tmp_path):
+    import json
+
+    from pippy_b200.schedules import measured_trace, simulated_trace, simulate, write_chrome_trace, zero_bubble
+
+    P, v, n = 4, 2, 8
+    sched = zero_bubble(P, v, n)
+    res = simulate(sched, lambda s: s % P, P * v, cost={Op.F: 2.0, Op.I: 3.0, Op.W: 2.0, Op.B: 5.0})
+    events = simulated_trace(res)
+    assert len(events) == sum(len(t) for t in res.timeline.values())
+    assert {e["tid"] for e in events} == set(range(P))
+    # rows never overlap in time: a rank runs one action at a time
+    for r in range(P):
+        rows = sorted((e["ts"], e["ts"] + e["dur"]) for e in events if e["tid"] == r)
+        assert all(a[1] <= b[0] + 1e-6 for a, b in zip(rows, rows[1:]))
+    stats = {"timeline": [("F(s0,mb0)", 0.0, 0.001), ("B(s0,mb0)", 0.002, 0.004)]}
+    ev = measured_trace(stats, rank=3)
+    assert ev[1]["ts"] == pytest.approx(2000.0) and ev[1]["dur"] == pytest.approx(2000.0) and ev[1]["tid"] == 3
+    path = tmp_path / "trace.json"
+    write_chrome_trace(str(path), events + ev, {r: f"rank {r}" for r in range(P)})
+    data = json.loads(path.read_text())
+    assert len(data["traceEvents"]) == len(events) + len(ev) + P
