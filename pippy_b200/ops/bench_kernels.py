@@ -3,6 +3,7 @@
     python -m pippy_b200.ops.bench_kernels gemm
     python -m pippy_b200.ops.bench_kernels attention
     python -m pippy_b200.ops.bench_kernels attention-once     # two forward+backward calls on a small case, for ncu
+    python -m pippy_b200.ops.bench_kernels gemm-once          # three launches of one GEMM, for ncu
     python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe
 
 Library rates (cuBLAS via torch.matmul, SDPA) are printed beside ours for scale.
@@ -50,6 +51,20 @@ def bench_gemm():
             print(f"gemm {what:22s} M{M} N{N} K{K} variant {variant}: {ms:.3f} ms {2 * M * N * K / ms / 1e9:.0f} TFLOP/s")
         ms = _time(lambda: torch.matmul(A, B))
         print(f"     torch.matmul (cuBLAS) for scale:                 {ms:.3f} ms {2 * M * N * K / ms / 1e9:.0f} TFLOP/s")
+
+
+def gemm_once():
+    """Three launches of the CTA-pair GEMM on one Llama-7B forward shape (operands 64 + 96 MB, output 192 MB), for ncu."""
+    from .gemm import gemm
+
+    M, N, K = 8192, 12288, 4096
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm(a, b, out=c, variant=2)
+    torch.cuda.synchronize()
+    print("done")
 
 
 def _attn_inputs(B, S, Hq, Hkv, D):
@@ -302,7 +317,7 @@ def bench_moe():
 
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
+    {"gemm": bench_gemm, "gemm-once": gemm_once, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
      "dp": bench_dp, "moe": bench_moe}[what]()
     from . import _lib
 

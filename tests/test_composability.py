@@ -71,3 +71,74 @@ def _pp_dp(rank, world, schedule):
 @pytest.mark.parametrize("schedule", ["1f1b", "zero_bubble"])
 def test_pp2_dp2_gpt2_tied_weights_and_grad_reduce(schedule):
     run_ranks(_pp_dp, 4, schedule, timeout_s=240)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Stage modules wrapped by PyTorch's own data-parallel containers (reference test/test_composability.py:203-368:
+# DDP | FSDP x gpipe | 1f1b | looped_bfs | interleaved_1f1b on a 2 x 2 mesh; gradients equal the single-process
+# gradients averaged over the replicas).  The runtime must keep them from reducing on every microbatch.
+D_HID = 16
+
+
+def _wrapped(rank, world, wrapper, schedule_name):
+    import copy
+
+    import torch.distributed as dist
+    import torch.nn as nn
+    from torch.distributed.device_mesh import DeviceMesh
+
+    import pippy_b200 as pp
+    from pippy_b200.parallel.mesh import init_mesh
+
+    mesh = init_mesh(pp_size=2, dp_size=2)
+    torch.manual_seed(0)
+    n_local = 1 if schedule_name in ("ScheduleGPipe", "Schedule1F1B") else 2
+    n_stages = 2 * n_local
+    blocks = [nn.Sequential(nn.Linear(D_HID, D_HID), nn.Tanh(), nn.Linear(D_HID, D_HID)) for _ in range(n_stages)]
+    reference = copy.deepcopy(nn.Sequential(*blocks))
+    n_mb, batch = 4, 8
+    gen = torch.Generator().manual_seed(7)
+    xs = [torch.randn(batch, D_HID, generator=gen) for _ in range(2)]
+    ys = [torch.randn(batch, D_HID, generator=gen) for _ in range(2)]
+    x, y = xs[mesh.dp_rank], ys[mesh.dp_rank]
+
+    dp_ranks = dist.get_process_group_ranks(mesh.dp_group)
+    stages = []
+    for k in range(n_local):
+        idx = mesh.pp_rank + 2 * k
+        mod = blocks[idx]
+        if wrapper == "ddp":
+            mod = nn.parallel.DistributedDataParallel(mod, process_group=mesh.dp_group)
+        else:
+            from torch.distributed.fsdp import fully_shard
+
+            fully_shard(mod, mesh=DeviceMesh.from_group(mesh.dp_group, "cpu", mesh=dp_ranks, mesh_dim_names=("dp",)))
+        stages.append(pp.ManualPipelineStage(mod, idx, n_stages, torch.device("cpu"), n_mb,
+                                             input_args=torch.empty(batch // n_mb, D_HID), group=mesh.pp_group))
+    loss_fn = nn.MSELoss(reduction="sum")
+    cls = getattr(pp, schedule_name)
+    schedule = cls(stages[0] if n_local == 1 else stages, n_mb, loss_fn=loss_fn)
+    first, last = mesh.pp_rank == 0, mesh.pp_rank == 1
+    losses = []
+    if first and not last:
+        schedule.step(x)
+    elif last:
+        schedule.step(target=y, losses=losses)
+
+    # oracle: the whole model on both replicas' batches; DDP and FSDP average over the replicas
+    for d in range(2):
+        (loss_fn(reference(xs[d]), ys[d]) / 2).backward()
+    for st in stages:
+        want = dict(reference[st.stage_index].named_parameters())
+        inner = st.submod.module if wrapper == "ddp" else st.submod
+        for name, p in inner.named_parameters():
+            got = p.grad.full_tensor() if hasattr(p.grad, "full_tensor") else p.grad
+            torch.testing.assert_close(got, want[name].grad, rtol=1e-4, atol=1e-5,
+                                       msg=f"{wrapper} {schedule_name} stage {st.stage_index} {name}")
+    dist.barrier()
+
+
+@pytest.mark.parametrize("wrapper", ["ddp", "fsdp"])
+@pytest.mark.parametrize("schedule_name", ["ScheduleGPipe", "Schedule1F1B", "ScheduleInterleaved1F1B"])
+def test_pp2_dp2_with_torch_data_parallel_wrappers(wrapper, schedule_name):
+    run_ranks(_wrapped, 4, wrapper, schedule_name, timeout_s=240)
