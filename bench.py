@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--schedule", default=None, help="interleaved_1f1b | zero_bubble | 1f1b | gpipe | looped_bfs")
+    ap.add_argument("--schedule", default=None, help="interleaved_1f1b | zero_bubble | zbv | 1f1b | gpipe | looped_bfs")
     ap.add_argument("--model", default="llama2-7b", help="llama2-7b | llama-small (for quick checks only)")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--seq", type=int, default=4096)

@@ -31,6 +31,7 @@ from .schedules import (  # noqa: F401
     ScheduleInterleaved1F1B,
     ScheduleInterleavedZeroBubble,
     ScheduleLoopedBFS,
+    ScheduleZBVZeroBubble,
     ScheduleZeroBubble,
 )
 

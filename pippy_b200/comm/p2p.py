@@ -88,14 +88,17 @@ class LinkGroups:
         return self.groups.get((src, dst, kind))
 
 
-def pipeline_links(num_stages: int, pp_size: int, dests: Optional[Dict[int, List[int]]] = None) -> List[Tuple[int, int]]:
-    """Directed rank pairs (producer rank, consumer rank) of a pipeline whose stage s lives on rank s % pp_size."""
+def pipeline_links(num_stages: int, pp_size: int, dests: Optional[Dict[int, List[int]]] = None,
+                   stage_to_rank: Optional[Dict[int, int]] = None) -> List[Tuple[int, int]]:
+    """Directed rank pairs (producer rank, consumer rank) of a pipeline; stage s lives on rank
+    ``stage_to_rank[s]``, by default s % pp_size."""
     out = []
     if dests is None:
         dests = {s: ([s + 1] if s + 1 < num_stages else []) for s in range(num_stages)}
+    where = (lambda s: stage_to_rank[s]) if stage_to_rank is not None else (lambda s: s % pp_size)
     for s, ds in dests.items():
         for d in ds:
-            a, b = s % pp_size, d % pp_size
-            if a != b:
+            a, b = where(s), where(d)
+            if a != b and (a, b) not in out:
                 out.append((a, b))
     return out

@@ -131,9 +131,10 @@ def unit_costs(cfg: LlamaConfig, seq_len: int):
     return attn, ffn, head, 0.02 * (attn + ffn)
 
 
-def balanced_partition(cfg: LlamaConfig, num_stages: int, pp_size: int, seq_len: int = 4096):
+def balanced_partition(cfg: LlamaConfig, num_stages: int, pp_size: int, seq_len: int = 4096, stage_to_rank=None):
     """Cuts the sequence [embed, attn0, mlp0, attn1, mlp1, ..., head] into ``num_stages`` contiguous stages so that
-    the most loaded RANK (stage s lives on rank s % pp_size) carries as little as possible.  Boundaries may fall
+    the most loaded RANK (stage s lives on rank ``stage_to_rank[s]``, by default s % pp_size) carries as little as
+    possible.  Boundaries may fall
     between a layer's attention and MLP.  Returns, per stage, a list of ``(layer, has_attention, has_ffn)``.
 
     With whole layers only, the head (worth most of a layer) always lands on top of a full share of layers; at
@@ -161,7 +162,7 @@ def balanced_partition(cfg: LlamaConfig, num_stages: int, pp_size: int, seq_len:
     def max_rank_load(bounds):
         loads = [0.0] * pp_size
         for s in range(num_stages):
-            loads[s % pp_size] += stage_cost(bounds, s)
+            loads[stage_to_rank[s] if stage_to_rank is not None else s % pp_size] += stage_cost(bounds, s)
         return max(loads), sum(l * l for l in loads)
 
     total = prefix[-1] + head + embed
@@ -230,11 +231,12 @@ class LlamaStage(nn.Module):
 
 
 def build_llama_stage(cfg: LlamaConfig, stage: int, num_stages: int, device=None, dtype=torch.bfloat16,
-                      pp_size: Optional[int] = None, seq_len: int = 4096, balance: bool = True) -> LlamaStage:
+                      pp_size: Optional[int] = None, seq_len: int = 4096, balance: bool = True,
+                      stage_to_rank=None) -> LlamaStage:
     """Stage ``stage`` of ``num_stages``. With ``balance`` (and a known ``pp_size``) layers are assigned by
     :func:`balanced_partition`; otherwise evenly by whole layers."""
     if balance and pp_size is not None and num_stages > 1:
-        parts = balanced_partition(cfg, num_stages, pp_size, seq_len)[stage]
+        parts = balanced_partition(cfg, num_stages, pp_size, seq_len, stage_to_rank)[stage]
     else:
         parts = list(layer_range(cfg.n_layers, stage, num_stages))
     return LlamaStage(cfg, parts, stage == 0, stage == num_stages - 1, device=device, dtype=dtype)

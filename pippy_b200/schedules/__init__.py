@@ -1,5 +1,15 @@
 from .actions import Action, Op, Schedule, add_send_recv, dump_csv, format_schedule, load_csv, validate
-from .generators import gpipe, interleaved_1f1b, looped_bfs, one_f_one_b, with_reduce_grad, zero_bubble
+from .generators import (
+    gpipe,
+    interleaved_1f1b,
+    looped_bfs,
+    one_f_one_b,
+    tuned_zero_bubble_placed,
+    v_placement,
+    with_reduce_grad,
+    zero_bubble,
+    zero_bubble_placed,
+)
 from .runtime import (
     PipelineSchedule,
     PipelineScheduleMulti,
@@ -10,6 +20,7 @@ from .runtime import (
     ScheduleInterleavedZeroBubble,
     ScheduleLoopedBFS,
     ScheduleTimeout,
+    ScheduleZBVZeroBubble,
     ScheduleZeroBubble,
     sorted_batch_isend_irecv,
 )

@@ -216,3 +216,131 @@ def with_reduce_grad(schedule: Schedule) -> Schedule:
                     new.append(Action(s, Op.REDUCE_GRAD))
         out[r] = new
     return out
+
+
+def v_placement(P: int) -> Dict[int, int]:
+    """Stage -> rank map of the V shape: rank r holds stage r on the way down and stage 2P-1-r on the way up, so
+    the first and the last stage share rank 0 and the turn (stages P-1, P) is a local hand-over on rank P-1."""
+    return {s: (s if s < P else 2 * P - 1 - s) for s in range(2 * P)}
+
+
+def zero_bubble_placed(
+    P: int,
+    placement: Dict[int, int],
+    n_mb: int,
+    extra_in_flight: int = 0,
+    max_pending_w: Optional[int] = None,
+    cost_f: int = 2,
+    cost_i: int = 3,
+    cost_w: int = 2,
+) -> Schedule:
+    """Zero-bubble schedule for an arbitrary stage -> rank placement, by greedy list scheduling on a timeline.
+
+    No per-rank order is assumed (the wrap-around generator above takes its orders from interleaved 1F1B): whenever
+    a rank is free it takes, in this order of preference, a ready input-gradient pass (oldest microbatch first, the
+    stage nearest the loss first), a parked weight-gradient pass if more than ``max_pending_w`` are parked, a ready
+    forward (the stage nearest the loss first, so that microbatches reach the loss and start their backward early)
+    while that STAGE holds fewer than ``S - s + extra_in_flight`` microbatches (the 1F1B bound per stage: a limit per
+    rank can fill up with early-stage microbatches and starve the stage they must pass next), and otherwise the
+    oldest parked weight gradient.  With ``v_placement(P)`` this gives the V-shaped zero-bubble schedule (upstream's ZBV,
+    torch/distributed/pipelining/schedules.py:2811-3000): at costs F = I = W it has no bubble beyond the fill, and
+    rank 0 holds both the embedding and the LM head.
+    """
+    S = len(placement)
+    if sorted(placement) != list(range(S)):
+        raise ValueError("placement must map stages 0..S-1")
+    local: Dict[int, List[int]] = {r: sorted((s for s in placement if placement[s] == r), reverse=True) for r in range(P)}
+    if any(not local[r] for r in range(P)):
+        raise ValueError("every rank needs at least one stage")
+    cap = {s: min(n_mb, S - s + extra_in_flight) for s in range(S)}
+    if max_pending_w is None:
+        max_pending_w = max(2 * P, 4)
+    next_f = {s: 0 for s in range(S)}
+    next_i = {s: 0 for s in range(S)}
+    wq: Dict[int, List] = {r: [] for r in range(P)}
+    in_flight = {s: 0 for s in range(S)}
+    busy_until = {r: 0 for r in range(P)}
+    finish: Dict[tuple, int] = {}
+    out: Schedule = {r: [] for r in range(P)}
+    remaining = 3 * S * n_mb
+    t = 0
+    guard = 0
+    INF = 1 << 60
+    while remaining > 0:
+        guard += 1
+        if guard > 200 * S * n_mb + 1000:
+            raise RuntimeError("zero-bubble list scheduling failed to converge")
+        for r in range(P):
+            if busy_until[r] > t:
+                continue
+            choice = None
+            ready_i = []
+            for s in local[r]:
+                m = next_i[s]
+                if m < n_mb and finish.get((s, "F", m), INF) <= t and (s == S - 1 or finish.get((s + 1, "I", m), INF) <= t):
+                    ready_i.append((m, -s, s))
+            if ready_i:
+                m, _, s = min(ready_i)
+                choice = ("I", s, m)
+            if choice is None and len(wq[r]) > max_pending_w:
+                choice = ("W",) + wq[r][0]
+            if choice is None:
+                for s in local[r]:  # nearest the loss first
+                    m = next_f[s]
+                    if m < n_mb and in_flight[s] < cap[s] and (s == 0 or finish.get((s - 1, "F", m), INF) <= t):
+                        choice = ("F", s, m)
+                        break
+            if choice is None and wq[r]:
+                choice = ("W",) + wq[r][0]
+            if choice is None:
+                continue
+            kind, s, m = choice
+            if kind == "F":
+                next_f[s] += 1
+                in_flight[s] += 1
+                dur = cost_f
+                out[r].append(Action(s, Op.F, m))
+            elif kind == "I":
+                next_i[s] += 1
+                in_flight[s] -= 1
+                wq[r].append((s, m))
+                dur = cost_i
+                out[r].append(Action(s, Op.I, m))
+            else:
+                wq[r].pop(0)
+                dur = cost_w
+                out[r].append(Action(s, Op.W, m))
+            finish[(s, kind, m)] = t + dur
+            busy_until[r] = t + dur
+            remaining -= 1
+        t += 1
+    return out
+
+
+def tuned_zero_bubble_placed(
+    P: int,
+    placement: Dict[int, int],
+    n_mb: int,
+    cost_f: int = 2,
+    cost_i: int = 3,
+    cost_w: int = 2,
+    extra_in_flight: tuple = (0, 2, 4),
+    pending_w: Optional[tuple] = None,
+    slack: float = 0.01,
+) -> Schedule:
+    """Greedy list scheduling is sensitive to its two limits, so a few settings are replayed on the cost model; of
+    those within ``slack`` of the shortest makespan the one that holds the fewest activations is kept."""
+    from .simulator import simulate
+
+    S = len(placement)
+    pending_w = pending_w or (P, 2 * P, 4 * P)
+    cost = {Op.F: float(cost_f), Op.I: float(cost_i), Op.W: float(cost_w), Op.B: float(cost_i + cost_w)}
+    tried = []
+    for extra in extra_in_flight:
+        for mpw in pending_w:
+            sched = zero_bubble_placed(P, placement, n_mb, extra, mpw, cost_f, cost_i, cost_w)
+            res = simulate(sched, lambda s: placement[s], S, cost=cost)
+            tried.append((res.makespan, max(res.peak_in_flight.values()), max(res.peak_pending_w.values()), sched))
+    shortest = min(t[0] for t in tried)
+    close = [t for t in tried if t[0] <= shortest * (1.0 + slack)]
+    return min(close, key=lambda t: (t[1], t[2], t[0]))[3]

@@ -163,7 +163,8 @@ class PipelineSchedule:
         if dist.is_available() and dist.is_initialized() and self.pp_group_size > 1 and use_link_groups:
             from ..comm.p2p import LinkGroups, pipeline_links
 
-            links = pipeline_links(self.num_stages, self.pp_group_size, self._topology())
+            links = pipeline_links(self.num_stages, self.pp_group_size, self._topology(),
+                                   first.stage_index_to_group_rank)
             # communicators are expensive: stages built once keep theirs across schedule objects
             self.link_groups = first.link_groups if first.link_groups is not None else LinkGroups(first.group, links)
             for st in self._stages:
@@ -177,7 +178,7 @@ class PipelineSchedule:
         raise NotImplementedError
 
     def _stage_to_rank(self, stage: int) -> int:
-        return stage % self.pp_group_size
+        return self._stages[0].stage_index_to_group_rank[stage]
 
     def _topology(self) -> Optional[Dict[int, List[int]]]:
         topo = getattr(self._stages[0], "global_dests", None)
@@ -506,3 +507,35 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
 
 
 ScheduleZeroBubble = ScheduleInterleavedZeroBubble
+
+
+class ScheduleZBVZeroBubble(PipelineSchedule):
+    """Zero-bubble schedule on the V-shaped placement: rank r holds stage r and stage 2P-1-r, so the first and the
+    last stage (embedding and LM head, a tied pair in many models) share rank 0 and the turn of the V is a local
+    hand-over.  Upstream's ScheduleZBVZeroBubble (torch/distributed/pipelining/schedules.py:2811-3000) hard-codes
+    its order; here the order comes from list scheduling on the cost model (``generators.tuned_zero_bubble_placed``).
+    The stages' placement is set by this constructor."""
+
+    def __init__(self, stages, n_microbatches, loss_fn=None, output_merge_spec=None, cost_f=2, cost_i=3, cost_w=2, **kw):
+        stages = list(stages)
+        if len(stages) != 2:
+            raise ValueError(f"ScheduleZBVZeroBubble needs exactly 2 stages per rank, got {len(stages)}")
+        first = min(stages, key=lambda s: s.stage_index)
+        P = first.group_size
+        placement = generators.v_placement(P)
+        expected = sorted(s for s, r in placement.items() if r == first.group_rank)
+        got = sorted(s.stage_index for s in stages)
+        if first.num_stages != 2 * P or got != expected:
+            raise ValueError(f"rank {first.group_rank} must hold stages {expected} of {2 * P} for the V shape, got {got}")
+        for st in stages:
+            st.set_placement(placement)
+        self._costs = (cost_f, cost_i, cost_w)
+        super().__init__(stages, n_microbatches, loss_fn, output_merge_spec, **kw)
+
+    def _compute_order(self) -> Schedule:
+        placement = self._stages[0].stage_index_to_group_rank
+        if not self._has_backward:
+            # forward only: every rank runs its stages' forwards in dependency order, nearest the loss first
+            order = generators.zero_bubble_placed(self.pp_group_size, placement, self._n_microbatches)
+            return {r: [a for a in acts if a.op == Op.F] for r, acts in order.items()}
+        return generators.tuned_zero_bubble_placed(self.pp_group_size, placement, self._n_microbatches, *self._costs)

@@ -136,6 +136,27 @@ class PipelineStageBase:
     def rank_of_stage(self, stage: int) -> int:
         return self.stage_index_to_group_rank[stage]
 
+    def set_placement(self, stage_to_rank: Dict[int, int]) -> None:
+        """Replaces the wrap-around stage -> group-rank map (stage i on rank i % group_size, reference
+        _PipelineStage.py:129-136) by another one, e.g. the V shape of ``schedules.generators.v_placement``.  Must
+        be the same on every rank and is set before a schedule is built on the stage."""
+        if sorted(stage_to_rank) != list(range(self.num_stages)):
+            raise ValueError(f"placement must map stages 0..{self.num_stages - 1}")
+        if any(not 0 <= r < self.group_size for r in stage_to_rank.values()):
+            raise ValueError(f"placement names a rank outside the pipeline group of {self.group_size}")
+        if stage_to_rank[self.stage_index] != self.group_rank:
+            raise ValueError(
+                f"placement puts stage {self.stage_index} on rank {stage_to_rank[self.stage_index]}, but it was "
+                f"built on rank {self.group_rank}"
+            )
+        self.stage_index_to_group_rank = dict(stage_to_rank)
+        # which inputs arrive over the wire depends on the placement: receive buffers are rebuilt on next use
+        chunks, self.chunks = self.chunks, None
+        self.args_recv_info = {}
+        self.grad_recv_info = {}
+        if chunks is not None:
+            self._prepare_forward_infra(chunks)
+
     def _global_rank(self, group_rank: int) -> int:
         if self.group is None:
             return group_rank

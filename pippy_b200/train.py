@@ -20,6 +20,7 @@ from .schedules import (
     ScheduleGPipe,
     ScheduleInterleaved1F1B,
     ScheduleInterleavedZeroBubble,
+    ScheduleZBVZeroBubble,
     ScheduleLoopedBFS,
 )
 
@@ -29,6 +30,7 @@ SCHEDULES = {
     "looped_bfs": ScheduleLoopedBFS,
     "interleaved_1f1b": ScheduleInterleaved1F1B,
     "zero_bubble": ScheduleInterleavedZeroBubble,
+    "zbv": ScheduleZBVZeroBubble,  # V-shaped placement: rank r holds stages r and 2P-1-r
 }
 
 
@@ -96,11 +98,20 @@ def build_llama_pipeline(
     mb = global_batch // n_microbatches
     stages: List[ManualPipelineStage] = []
     params = []
-    for k in range(virtual_stages):
-        s = pp_rank + k * pp_size
+    placement = None
+    if schedule == "zbv":
+        if virtual_stages != 2:
+            raise ValueError("the V-shaped schedule runs exactly 2 stages per rank")
+        from .schedules import v_placement
+
+        placement = v_placement(pp_size)
+    held = (sorted(s for s, r in placement.items() if r == pp_rank) if placement is not None
+            else [pp_rank + k * pp_size for k in range(virtual_stages)])
+    last_rank = placement[num_stages - 1] if placement is not None else (num_stages - 1) % pp_size
+    for s in held:
         torch.manual_seed(seed + s)
         module = build_llama_stage(cfg, s, num_stages, device=device, dtype=dtype, pp_size=pp_size, seq_len=seq_len,
-                                   balance=balance)
+                                   balance=balance, stage_to_rank=placement)
         inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
         out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1
@@ -126,7 +137,7 @@ def build_llama_pipeline(
     else:
         sched = cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
-                    holds_last=((num_stages - 1) % pp_size == pp_rank))
+                    holds_last=(last_rank == pp_rank))
 
 
 def build_gpt2_pipeline(

@@ -142,3 +142,45 @@ def _wrapped(rank, world, wrapper, schedule_name):
 @pytest.mark.parametrize("schedule_name", ["ScheduleGPipe", "Schedule1F1B", "ScheduleInterleaved1F1B"])
 def test_pp2_dp2_with_torch_data_parallel_wrappers(wrapper, schedule_name):
     run_ranks(_wrapped, 4, wrapper, schedule_name, timeout_s=240)
+
+
+def _llama_v_shape(rank, world):
+    """The V-shaped zero-bubble schedule trains the same Llama as the wrap-around one: same loss, same updated
+    parameters per stage (stage modules are seeded by stage index, so both placements build identical weights)."""
+    import torch.distributed as dist
+
+    from pippy_b200.models.llama import LlamaConfig
+    from pippy_b200.train import build_llama_pipeline
+
+    cfg = LlamaConfig(vocab_size=64, dim=32, n_layers=4, n_heads=2, ffn_dim=64)
+    B, S, n_mb = 4, 16, 4
+    gen = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=gen)
+    results = {}
+    for schedule in ("zero_bubble", "zbv"):
+        pipe = build_llama_pipeline(cfg, B, S, n_mb, torch.device("cpu"), schedule=schedule, virtual_stages=2,
+                                    dtype=torch.float32, lr=1e-2, weight_decay=0.0, balance=False)
+        assert pipe.holds_first == (rank == 0)
+        assert pipe.holds_last == ((rank == 0) if schedule == "zbv" else (rank == world - 1))
+        loss = pipe.train_step(inputs=ids if pipe.holds_first else None, target=ids if pipe.holds_last else None)
+        state = {st.stage_index: {k: v.detach().clone() for k, v in st.submod.state_dict().items()} for st in pipe.stages}
+        results[schedule] = (None if loss is None else float(loss), state)
+    # gather every stage's updated parameters and the loss from whichever rank holds them
+    gathered = [None] * world
+    dist.all_gather_object(gathered, results)
+    merged = {sch: {} for sch in ("zero_bubble", "zbv")}
+    losses = {}
+    for part in gathered:
+        for sch, (loss, state) in part.items():
+            merged[sch].update(state)
+            if loss is not None:
+                losses[sch] = loss
+    assert sorted(merged["zbv"]) == sorted(merged["zero_bubble"]) == [0, 1, 2, 3]
+    assert abs(losses["zbv"] - losses["zero_bubble"]) < 1e-5
+    for s in range(4):
+        for k, v in merged["zero_bubble"][s].items():
+            torch.testing.assert_close(merged["zbv"][s][k], v, rtol=1e-5, atol=1e-6, msg=f"stage {s} {k}")
+
+
+def test_llama_v_shaped_schedule_matches_wrap_around():
+    run_ranks(_llama_v_shape, 2, timeout_s=240)

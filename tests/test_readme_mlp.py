@@ -48,29 +48,33 @@ def _run(rank, world, schedule_name, v):
     in_dims = {0: 512}
     dims = [512, 512, 1024, 256, 10]
     per = 4 // num_stages
-    for k in range(v):
-        s = rank + k * world
+    v_shape = schedule_name == "zbv"  # rank r holds stages r and 2P-1-r
+    held = sorted(st for st, r in pp.schedules.v_placement(world).items() if r == rank) if v_shape else \
+        [rank + k * world for k in range(v)]
+    last_rank = 0 if v_shape else (num_stages - 1) % world
+    for s in held:
         inp = torch.empty(64 // n_mb, dims[s * per], device="meta")
         stages.append(pp.ManualPipelineStage(mods[s].to("cpu"), s, num_stages, torch.device("cpu"), n_mb,
                                              input_args=inp.to("cpu") if False else torch.empty(64 // n_mb, dims[s * per])))
     cls = {
         "gpipe": pp.ScheduleGPipe, "1f1b": pp.Schedule1F1B, "bfs": pp.ScheduleLoopedBFS,
         "interleaved": pp.ScheduleInterleaved1F1B, "zb": pp.ScheduleInterleavedZeroBubble,
+        "zbv": pp.ScheduleZBVZeroBubble,
     }[schedule_name]
     sched = cls(stages[0] if v == 1 and schedule_name in ("gpipe", "1f1b") else stages, n_mb, loss_fn=loss_fn)
     losses = []
     for it in range(2):  # second iteration checks state is reset between steps
         for st in stages:
             st.submod.zero_grad()
-        if rank == 0 and rank == (num_stages - 1) % world:
+        if rank == 0 and rank == last_rank:
             out = sched.step(x, target=y, losses=losses)
         elif rank == 0:
             out = sched.step(x)
-        elif rank == (num_stages - 1) % world:
+        elif rank == last_rank:
             out = sched.step(target=y, losses=losses)
         else:
             out = sched.step()
-    if rank == (num_stages - 1) % world:
+    if rank == last_rank:
         torch.testing.assert_close(out, ref(x))
         torch.testing.assert_close(torch.stack(losses).sum(), ref_loss)
     ref_params = dict(ref.named_parameters())
@@ -85,6 +89,7 @@ def _run(rank, world, schedule_name, v):
     dist.barrier()
 
 
-@pytest.mark.parametrize("schedule_name,v", [("gpipe", 1), ("1f1b", 1), ("zb", 1), ("bfs", 2), ("interleaved", 2), ("zb", 2)])
+@pytest.mark.parametrize("schedule_name,v", [("gpipe", 1), ("1f1b", 1), ("zb", 1), ("bfs", 2), ("interleaved", 2), ("zb", 2),
+                                             ("zbv", 2)])
 def test_readme_mlp_two_ranks(schedule_name, v):
     run_ranks(_run, 2, schedule_name, v)

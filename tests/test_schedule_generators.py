@@ -146,3 +146,32 @@ def test_chrome_trace_of_simulated_and_measured_timelines(tmp_path):
     write_chrome_trace(str(path), events + ev, {r: f"rank {r}" for r in range(P)})
     data = json.loads(path.read_text())
     assert len(data["traceEvents"]) == len(events) + len(ev) + P
+
+
+@pytest.mark.parametrize("P,n", [(2, 2), (2, 8), (3, 5), (4, 4), (4, 16), (8, 8), (8, 32)])
+def test_v_shaped_zero_bubble_is_valid_and_beats_interleaved(P, n):
+    placement = G.v_placement(P)
+    assert placement[0] == placement[2 * P - 1] == 0 and placement[P - 1] == placement[P] == P - 1
+    cost = {Op.F: 2.0, Op.I: 3.0, Op.W: 2.0, Op.B: 5.0}
+    for extra in (0, 3):
+        for mpw in (1, P, 4 * P):
+            sched = G.zero_bubble_placed(P, placement, n, extra, mpw)       # never deadlocks, whatever the limits
+            A.validate(sched, 2 * P, n, lambda s: placement[s])
+            S.simulate(sched, lambda s: placement[s], 2 * P, cost=cost)
+    tuned = G.tuned_zero_bubble_placed(P, placement, n)
+    A.validate(tuned, 2 * P, n, lambda s: placement[s])
+    res = S.simulate(tuned, lambda s: placement[s], 2 * P, cost=cost)
+    if n % P == 0:
+        inter = S.simulate(G.interleaved_1f1b(P, 2, n), lambda s: s % P, 2 * P, cost=cost)
+        assert res.makespan <= inter.makespan
+    # both ends of the model on rank 0: the comm plan has no link between rank 0 and rank P-1 other than neighbours
+    with_comm = A.add_send_recv(tuned, lambda s: placement[s], 2 * P)
+    peer_ranks = {placement[a.peer] for a in with_comm[0] if a.op.is_comm and a.peer is not None}
+    assert peer_ranks <= {1}
+
+
+def test_placement_errors():
+    with pytest.raises(ValueError):
+        G.zero_bubble_placed(2, {0: 0, 1: 1, 3: 0}, 4)
+    with pytest.raises(ValueError):
+        G.zero_bubble_placed(2, {0: 0, 1: 0, 2: 0, 3: 0}, 4)
