@@ -85,6 +85,7 @@ def build_llama_pipeline(
     schedule_kwargs: Optional[dict] = None,
     balance: bool = True,
     dp_group: Optional[dist.ProcessGroup] = None,
+    activation_checkpointing: bool = False,
 ) -> Pipeline:
     """Builds this rank's Llama stages (stage ``rank + k * pp_size`` for k < virtual_stages), the schedule and
     the fused optimizer."""
@@ -111,7 +112,8 @@ def build_llama_pipeline(
     for s in held:
         torch.manual_seed(seed + s)
         module = build_llama_stage(cfg, s, num_stages, device=device, dtype=dtype, pp_size=pp_size, seq_len=seq_len,
-                                   balance=balance, stage_to_rank=placement)
+                                   balance=balance, stage_to_rank=placement,
+                                   activation_checkpointing=activation_checkpointing)
         inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
         out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1

@@ -184,3 +184,34 @@ def _llama_v_shape(rank, world):
 
 def test_llama_v_shaped_schedule_matches_wrap_around():
     run_ranks(_llama_v_shape, 2, timeout_s=240)
+
+
+def _llama_checkpointing(rank, world, schedule):
+    """Activation checkpointing changes what is kept, not what is computed: same loss and the same updated
+    parameters, also when the weight-gradient passes are deferred (zero-bubble)."""
+    import torch.distributed as dist
+
+    from pippy_b200.models.llama import LlamaConfig
+    from pippy_b200.train import build_llama_pipeline
+
+    cfg = LlamaConfig(vocab_size=64, dim=32, n_layers=4, n_heads=2, ffn_dim=64)
+    B, S, n_mb = 4, 16, 4
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(5))
+    out = {}
+    for ckpt in (False, True):
+        pipe = build_llama_pipeline(cfg, B, S, n_mb, torch.device("cpu"), schedule=schedule, virtual_stages=2,
+                                    dtype=torch.float32, lr=1e-2, weight_decay=0.0, activation_checkpointing=ckpt)
+        loss = pipe.train_step(inputs=ids if pipe.holds_first else None, target=ids if pipe.holds_last else None)
+        out[ckpt] = (None if loss is None else float(loss),
+                     [{k: v.detach().clone() for k, v in st.submod.state_dict().items()} for st in pipe.stages])
+    if out[False][0] is not None:
+        assert abs(out[False][0] - out[True][0]) < 1e-6
+    for a, b in zip(out[False][1], out[True][1]):
+        for k in a:
+            torch.testing.assert_close(b[k], a[k], rtol=1e-5, atol=1e-6, msg=k)
+    dist.barrier()
+
+
+@pytest.mark.parametrize("schedule", ["interleaved_1f1b", "zero_bubble"])
+def test_llama_activation_checkpointing_same_result(schedule):
+    run_ranks(_llama_checkpointing, 2, schedule, timeout_s=240)

@@ -236,3 +236,4 @@ def test_rope_attention_with_rotary():
     ref.backward(do.float())
     assert _rel(out, ref) < 2e-2
     assert _rel(qkv.grad, qf.grad) < 3e-2
+
