@@ -57,15 +57,15 @@ class _Watchdog:
 def main(args) -> None:
     ref_path = os.path.join(HERE, "_ref")
     if not os.path.isdir(os.path.join(ref_path, "pippy")):
-        _unavailable("baseline/_ref/pippy is missing: the offline install of /root/reference was not done on this box")
+        _unavailable("baseline/_ref/pippy is missing: the offline install of the reference was not done on this box")
         return
     if int(os.environ.get("WORLD_SIZE", "1")) >= 8:
         # Two attempts on 8 B200s completed no step: ScheduleInterleaved1F1B (killed by a 200 s timeout) and
-        # Schedule1F1B (no progress for 150 s, ended by the watchdog below); the logs are named in DESIGN.md.
+        # Schedule1F1B (no progress for 150 s, ended by the watchdog below).
         # All of a rank's transfers share one NCCL stream there, so a send that waits for its peer blocks the
         # receive the peer is waiting for.  The reference's GPU code is not run again at this size.
         _unavailable("the reference's schedules (interleaved 1F1B and 1F1B) blocked inside NCCL on 8 GPUs on this "
-                     "box and completed no step; not run again (see DESIGN.md)")
+                     "box and completed no step (two attempts); not run again")
         return
     try:
         _run(args, ref_path)
