@@ -62,3 +62,17 @@ def test_gpt2_example_runs_on_two_ranks():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "pipeline output equals the unsplit model" in res.stdout
+
+
+@pytest.mark.parametrize("name", ["gpt2", "bert", "mbart", "llama"])
+def test_family_trains_through_traced_stages(name):
+    """Forward + backward under 1F1B on two gloo ranks: loss and every parameter gradient equal the unsplit model's;
+    weights tied across stages are replicated and their gradients sum (GPT-2, BERT), encoder outputs skip over the
+    stage boundary into every decoder layer (mBART)."""
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+           "--nproc-per-node", "2", os.path.join(ROOT, "examples", "huggingface", "pippy_hf.py"), "--model", name,
+           "--train"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "parameter gradients" in res.stdout
