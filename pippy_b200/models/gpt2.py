@@ -127,7 +127,7 @@ class TiedEmbeddingSync:
     ``broadcast()`` once after initialisation, ``sync_grads()`` after every schedule step. Collective over the
     pipeline group at construction (a two-rank group is created)."""
 
-    def __init__(self, stages, pp_group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, stages, pp_group: Optional[dist.ProcessGroup] = None, last_rank: Optional[int] = None):
         self.first = next((s for s in stages if s.is_first), None)
         self.last = next((s for s in stages if s.is_last), None)
         self.pg = None
@@ -136,7 +136,8 @@ class TiedEmbeddingSync:
             return
         world = dist.get_world_size(pp_group)
         num_stages = stages[0].num_stages
-        r_first, r_last = 0, (num_stages - 1) % world
+        # wrap-around placement unless the caller says where the last stage lives (V shape: on rank 0 too)
+        r_first, r_last = 0, ((num_stages - 1) % world if last_rank is None else last_rank)
         from ..comm.p2p import new_groups_worldwide
 
         ranks = sorted({r_first, r_last})
@@ -173,4 +174,9 @@ class TiedEmbeddingSync:
             if p.grad is None:
                 p.grad = torch.zeros_like(p)
             g = p.grad
+        elif p.grad is not None:
+            # ops outside this package's kernels (the CPU path) leave their gradient in .grad: fold it in first,
+            # or the reduction would miss it and the two copies would drift apart
+            g.add_(p.grad.to(g.dtype))
+            p.grad = None
         dist.all_reduce(g, group=self.pg)

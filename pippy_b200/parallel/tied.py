@@ -38,7 +38,8 @@ class TiedParamSync:
         wanted, pending = [], []
         for group in pipe.replicated_params:
             stage_ids = sorted(int(name.split("_")[-1]) for name in group)
-            ranks = sorted({sid % world for sid in stage_ids})
+            where = (local_stages[0].rank_of_stage if local_stages else (lambda sid: sid % world))
+            ranks = sorted({where(sid) for sid in stage_ids})
             local = [(by_index[sid], group[f"submod_{sid}"]) for sid in stage_ids if sid in by_index]
             need = len(ranks) > 1 and rank in ranks
             if need:

@@ -171,8 +171,18 @@ def build_gpt2_pipeline(
     mb = global_batch // n_microbatches
     stages: List[ManualPipelineStage] = []
     params = []
-    for k in range(virtual_stages):
-        s = pp_rank + k * pp_size
+    placement = None
+    if schedule == "zbv":
+        # V shape: embedding and LM head share rank 0, so the tied weight needs no cross-rank synchronisation
+        if virtual_stages != 2:
+            raise ValueError("the V-shaped schedule runs exactly 2 stages per rank")
+        from .schedules import v_placement
+
+        placement = v_placement(pp_size)
+    held = (sorted(s for s, r in placement.items() if r == pp_rank) if placement is not None
+            else [pp_rank + k * pp_size for k in range(virtual_stages)])
+    last_rank = placement[num_stages - 1] if placement is not None else (num_stages - 1) % pp_size
+    for s in held:
         torch.manual_seed(seed + s)
         module = build_gpt2_stage(cfg, s, num_stages, device=device, dtype=dtype)
         inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
@@ -193,7 +203,7 @@ def build_gpt2_pipeline(
         if id(p_) not in seen:
             seen.add(id(p_))
             unique.append(p_)
-    tied = TiedEmbeddingSync(stages, group)
+    tied = TiedEmbeddingSync(stages, group, last_rank=last_rank)
     tied.broadcast()
     flat = FlatParams(unique)
     opt = FusedAdamW(flat, lr=lr, weight_decay=weight_decay)
@@ -206,7 +216,7 @@ def build_gpt2_pipeline(
     kw = dict(loss_fn=gpt2_loss(cfg), grad_reducer=reducer, record_timing=record_timing)
     sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
-                    holds_last=((num_stages - 1) % pp_size == pp_rank), tied=tied)
+                    holds_last=(last_rank == pp_rank), tied=tied)
 
 
 def build_mixtral_pipeline(

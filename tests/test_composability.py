@@ -215,3 +215,46 @@ def _llama_checkpointing(rank, world, schedule):
 @pytest.mark.parametrize("schedule", ["interleaved_1f1b", "zero_bubble"])
 def test_llama_activation_checkpointing_same_result(schedule):
     run_ranks(_llama_checkpointing, 2, schedule, timeout_s=240)
+
+
+def _gpt2_v_shape(rank, world):
+    """GPT-2 with its tied embedding / LM head: on the V shape both ends live on rank 0, so the head simply uses the
+    embedding parameter; loss and updated parameters equal the wrap-around schedule's (which syncs the tied pair
+    across the first and last rank)."""
+    import torch.distributed as dist
+
+    from pippy_b200.models.gpt2 import GPT2Config
+    from pippy_b200.train import build_gpt2_pipeline
+
+    cfg = GPT2Config.tiny()
+    B, S, n_mb = 4, 16, 4
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(9))
+    results = {}
+    for schedule in ("zero_bubble", "zbv"):
+        pipe = build_gpt2_pipeline(cfg, B, S, n_mb, torch.device("cpu"), schedule=schedule, virtual_stages=2,
+                                   dtype=torch.float32, lr=1e-2, weight_decay=0.0)
+        if schedule == "zbv":
+            assert pipe.holds_first == pipe.holds_last == (rank == 0)
+            if rank == 0:
+                first = next(s for s in pipe.stages if s.is_first)
+                last = next(s for s in pipe.stages if s.is_last)
+                assert last.submod.lm_head.weight is first.submod.wte.weight
+        loss = pipe.train_step(inputs=ids if pipe.holds_first else None, target=ids if pipe.holds_last else None)
+        state = {st.stage_index: {k: v.detach().clone() for k, v in st.submod.state_dict().items()} for st in pipe.stages}
+        results[schedule] = (None if loss is None else float(loss), state)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, results)
+    merged, losses = {"zero_bubble": {}, "zbv": {}}, {}
+    for part in gathered:
+        for sch, (loss, state) in part.items():
+            merged[sch].update(state)
+            if loss is not None:
+                losses[sch] = loss
+    assert abs(losses["zbv"] - losses["zero_bubble"]) < 1e-5
+    for s in range(4):
+        for k, v in merged["zero_bubble"][s].items():
+            torch.testing.assert_close(merged["zbv"][s][k], v, rtol=1e-5, atol=1e-6, msg=f"stage {s} {k}")
+
+
+def test_gpt2_v_shaped_schedule_keeps_tied_weights_on_one_rank():
+    run_ranks(_gpt2_v_shape, 2, timeout_s=240)
