@@ -246,3 +246,42 @@ def _failing(rank, world):
 
 def test_stalled_neighbour_is_detected_by_bounded_wait():
     run_ranks(_failing, 2, timeout_s=60)
+
+
+def _v_shape_traced(rank, world):
+    """Traced stages on the V-shaped placement (rank r holds stages r and 2P-1-r): output, summed loss and every
+    parameter gradient equal the unsplit model; the input/weight gradient split runs through the generic
+    autograd-graph path because the stages are plain torch modules."""
+    import copy
+
+    import torch.nn as nn
+
+    import pippy_b200 as pp
+
+    torch.manual_seed(0)
+    model = nn.Sequential(*[nn.Sequential(nn.Linear(16, 16), nn.Tanh()) for _ in range(2 * world)])
+    ref = copy.deepcopy(model)
+    x, y = torch.randn(8, 16), torch.randn(8, 16)
+    pipe = pp.pipeline(model, 4, example_args=(x,), split_spec={str(i): pp.SplitPoint.END for i in range(2 * world - 1)})
+    placement = pp.schedules.v_placement(world)
+    stages = [pp.PipelineStage(pipe, s, torch.device("cpu")) for s, r in sorted(placement.items()) if r == rank]
+    loss_fn = nn.MSELoss(reduction="sum")
+    sched = pp.ScheduleZBVZeroBubble(stages, 4, loss_fn=loss_fn)
+    losses = []
+    if rank == 0:  # first and last stage
+        out = sched.step(x, target=y, losses=losses)
+        torch.testing.assert_close(out, ref(x), rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(torch.stack(losses).sum(), loss_fn(ref(x), y), rtol=1e-4, atol=1e-5)
+    else:
+        assert sched.step() is None
+    loss_fn(ref(x), y).backward()
+    want = dict(ref.named_parameters())
+    for st in stages:
+        for n, p in st.submod.named_parameters():
+            torch.testing.assert_close(p.grad, want[n].grad, rtol=1e-4, atol=1e-5, msg=n)
+    with pytest.raises(ValueError):
+        stages[0].set_placement({s: 0 for s in range(2 * world)} if rank else {s: 1 for s in range(2 * world)})
+
+
+def test_traced_stages_on_v_shaped_placement_three_ranks():
+    run_ranks(_v_shape_traced, 3)
