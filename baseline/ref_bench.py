@@ -1,6 +1,15 @@
-"""Reference arm of bench.py: the UNMODIFIED reference (installed under baseline/_ref) driving a stock PyTorch
-model through its own public API (ManualPipelineStage + Schedule1F1B / ScheduleInterleaved1F1B) with
-torch.optim.AdamW, on the same config, metric and timing rules as the main arm."""
+"""Reference arm of bench.py: the reference's own runtime driving a stock PyTorch model with torch.optim.AdamW,
+on the same config, metric and timing rules as the main arm.
+
+Two systems answer to "the reference", and the printed line names which one ran (``reference_system``):
+
+* ``pippy``: the UNMODIFIED reference installed under baseline/_ref, through its public API
+  (ManualPipelineStage + Schedule1F1B on one GPU, ScheduleInterleaved1F1B on two).
+* ``torch.distributed.pipelining``: the form the reference migrated into (its README says so), as shipped with the
+  installed torch: PipelineStage + ScheduleInterleaved1F1B, stock code path.  It runs where the reference's own
+  interleaved schedule completes no step (four or more ranks; see ``_pippy_blocks``).
+
+Both drive the same ``ref_model.Stage`` slices, the same optimizer and the same watchdog."""
 import json
 import os
 import sys
@@ -15,15 +24,22 @@ def _unavailable(why: str) -> None:
 
 
 class _Watchdog:
-    """Ends the process if the reference makes no progress: its schedules block inside NCCL when ranks fall out of
-    step, and a blocked rank would otherwise keep the whole job (and its GPUs) until an outer timeout."""
+    """Ends the process when the device stops completing steps, so that a blocked rank cannot keep the whole job
+    (and its GPUs) until an outer timeout.
 
-    def __init__(self, limit_s: float):
+    Progress is what the DEVICE finished, not what the host queued: after every step the caller records a CUDA event
+    (``mark``) and this thread polls ``event.query()``.  The limit starts generous (first step: context, NCCL
+    communicators, allocator warm-up) and is then derived from the measured step time (``set_step_time``)."""
+
+    def __init__(self, startup_limit_s: float, device=None):
         import threading
 
-        self.limit_s = limit_s
+        self.limit_s = startup_limit_s
+        self.device = device
         self.last = None
         self.what = "start-up"
+        self._events = []  # (event, label) recorded but not yet seen complete
+        self._lock = threading.Lock()
         self._stop = False
         self._thread = threading.Thread(target=self._run, daemon=True)
 
@@ -33,11 +49,17 @@ class _Watchdog:
         self.last = time.time()
         self._thread.start()
 
-    def kick(self, what: str):
-        import time
+    def mark(self, what: str):
+        """Records an event on the current stream; the watchdog counts it as progress once the device reaches it."""
+        import torch
 
-        self.last = time.time()
-        self.what = what
+        ev = torch.cuda.Event()
+        ev.record()
+        with self._lock:
+            self._events.append((ev, what))
+
+    def set_step_time(self, step_s: float, factor: float = 5.0, floor_s: float = 60.0):
+        self.limit_s = max(floor_s, factor * step_s)
 
     def stop(self):
         self._stop = True
@@ -45,36 +67,57 @@ class _Watchdog:
     def _run(self):
         import time
 
+        import torch
+
+        if self.device is not None:
+            torch.cuda.set_device(self.device)
         while not self._stop:
-            time.sleep(1.0)
+            time.sleep(0.5)
+            with self._lock:
+                while self._events and self._events[0][0].query():
+                    _, self.what = self._events.pop(0)
+                    self.last = time.time()
             if time.time() - self.last > self.limit_s:
-                _unavailable(f"the reference made no progress for {self.limit_s:.0f}s during {self.what} "
-                             "(its schedule blocked inside NCCL); run abandoned")
+                _unavailable(f"no step completed on the device for {self.limit_s:.0f}s after {self.what}; "
+                             "run abandoned by the arm's watchdog")
                 sys.stdout.flush()
                 os._exit(0)
 
 
+def _pippy_blocks(world: int) -> bool:
+    """The reference's ScheduleInterleaved1F1B completed no step at 4 ranks (no progress in the first step for
+    150 s, all four GPUs spinning) nor at 8 (ended by a 200 s timeout; its Schedule1F1B made no progress at 8
+    either).  Each rank issues its transfers as coalesced NCCL groups on one communicator, in program order, and in
+    its 1F1B phase one group mixes a step's receives with the previous step's sends to up to four peers
+    (pippy/PipelineSchedule.py:706-742); its own comment says the groups "need to be aligned to prevent a hang" and
+    its 4-GPU test is disabled as "not working" (test/test_pipeline_schedule.py:333-336).  A replay of the groups
+    per rank shows that the order completes only if a send may finish before its receiver's matching group reaches
+    the head of that rank's queue, i.e. it relies on how much NCCL buffers per connection; with 64 MiB activations
+    that held at 2 ranks and not at 4 or 8.  That code is not run again at those sizes."""
+    return world >= 4
+
+
 def main(args) -> None:
     ref_path = os.path.join(HERE, "_ref")
-    if not os.path.isdir(os.path.join(ref_path, "pippy")):
-        _unavailable("baseline/_ref/pippy is missing: the offline install of the reference was not done on this box")
-        return
-    if int(os.environ.get("WORLD_SIZE", "1")) >= 8:
-        # Two attempts on 8 B200s completed no step: ScheduleInterleaved1F1B (killed by a 200 s timeout) and
-        # Schedule1F1B (no progress for 150 s, ended by the watchdog below).
-        # All of a rank's transfers share one NCCL stream there, so a send that waits for its peer blocks the
-        # receive the peer is waiting for.  The reference's GPU code is not run again at this size.
-        _unavailable("the reference's schedules (interleaved 1F1B and 1F1B) blocked inside NCCL on 8 GPUs on this "
-                     "box and completed no step (two attempts); not run again")
-        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    system = os.environ.get("PIPPY_REF_SYSTEM") or ("torch.distributed.pipelining" if _pippy_blocks(world) else "pippy")
+    if system == "pippy":
+        if not os.path.isdir(os.path.join(ref_path, "pippy")):
+            _unavailable("baseline/_ref/pippy is missing: the offline install of the reference was not done on this box")
+            return
+        if _pippy_blocks(world):
+            _unavailable("the reference's own schedules blocked inside NCCL at 4 and 8 ranks on this pool and are not "
+                         "run again at those sizes")
+            return
     try:
-        _run(args, ref_path)
+        _run(args, ref_path, system)
     except Exception as e:  # report instead of failing the driver
         traceback.print_exc(file=sys.stderr)
         _unavailable(f"{type(e).__name__}: {e}")
 
 
-def _run(args, ref_path) -> None:
+def _run(args, ref_path, system: str) -> None:
+    import time
     import warnings
 
     warnings.filterwarnings("ignore")
@@ -82,10 +125,13 @@ def _run(args, ref_path) -> None:
     import torch.distributed as dist
     import torch.nn.functional as F
 
-    sys.path.insert(0, ref_path)
     sys.path.insert(0, HERE)
-    from pippy.ManualPipelineStage import ManualPipelineStage
-    from pippy.PipelineSchedule import Schedule1F1B, ScheduleInterleaved1F1B
+    if system == "pippy":
+        sys.path.insert(0, ref_path)
+        from pippy.ManualPipelineStage import ManualPipelineStage
+        from pippy.PipelineSchedule import Schedule1F1B, ScheduleInterleaved1F1B
+    else:
+        from torch.distributed.pipelining import PipelineStage, Schedule1F1B, ScheduleInterleaved1F1B
 
     import ref_model
     from bench import ClockSampler  # nvidia-smi sampling only; no model/engine code
@@ -121,22 +167,31 @@ def _run(args, ref_path) -> None:
         torch.manual_seed(s)
         mod = ref_model.Stage(range(s * per, (s + 1) * per), s == 0, s == num_stages - 1, vocab, dim, n_heads, ffn,
                               1e-5, 10000.0, args.seq, dtype, device)
-        inp = (torch.empty(mb, args.seq, dtype=torch.int64, device=device) if s == 0
-               else torch.empty(mb, args.seq, dim, dtype=dtype, device=device))
-        out = (torch.empty(mb, args.seq, vocab, dtype=dtype, device="meta") if s == num_stages - 1
-               else torch.empty(mb, args.seq, dim, dtype=dtype, device="meta"))
-        stages.append(ManualPipelineStage(mod, s, num_stages, device, n_mb, input_args=inp, output_args=out))
+        if system == "pippy":
+            inp = (torch.empty(mb, args.seq, dtype=torch.int64, device=device) if s == 0
+                   else torch.empty(mb, args.seq, dim, dtype=dtype, device=device))
+            out = (torch.empty(mb, args.seq, vocab, dtype=dtype, device="meta") if s == num_stages - 1
+                   else torch.empty(mb, args.seq, dim, dtype=dtype, device="meta"))
+            stages.append(ManualPipelineStage(mod, s, num_stages, device, n_mb, input_args=inp, output_args=out))
+            del inp
+        else:
+            inp = (torch.empty(mb, args.seq, dtype=torch.int64, device="meta") if s == 0
+                   else torch.empty(mb, args.seq, dim, dtype=dtype, device="meta"))
+            out = (torch.empty(mb, args.seq, vocab, dtype=dtype, device="meta") if s == num_stages - 1
+                   else torch.empty(mb, args.seq, dim, dtype=dtype, device="meta"))
+            stages.append(PipelineStage(mod, s, num_stages, device, input_args=(inp,), output_args=(out,)))
         params.extend(mod.parameters())
-        del inp
 
     def loss_fn(logits, target):
         return F.cross_entropy(logits.reshape(-1, logits.shape[-1]), target.reshape(-1), ignore_index=-100) / n_mb
 
+    # the loss already carries 1/n_mb, so upstream's own gradient scaling stays off
+    extra = {} if system == "pippy" else {"scale_grads": False}
     if virtual == 1:
-        sched = Schedule1F1B(stages[0], n_mb, loss_fn=loss_fn)
+        sched = Schedule1F1B(stages[0], n_mb, loss_fn=loss_fn, **extra)
         sched_name = "1f1b (single stage)"
     else:
-        sched = ScheduleInterleaved1F1B(stages, n_mb, loss_fn=loss_fn)
+        sched = ScheduleInterleaved1F1B(stages, n_mb, loss_fn=loss_fn, **extra)
         sched_name = "interleaved_1f1b"
     opt = torch.optim.AdamW(params, lr=3e-4, weight_decay=0.1, fused=True)
     holds_first = rank == 0
@@ -177,15 +232,18 @@ def _run(args, ref_path) -> None:
             dist.all_reduce(t, op=op)
         return float(t.item())
 
-    dog = _Watchdog(150.0)
+    dog = _Watchdog(300.0, device)
     dog.start()
     loss = None
     for i in range(args.warmup):
+        t0 = time.time()
         loss = step(dev_ids[i % 2], dev_lbl[i % 2])
+        dog.mark(f"warm-up step {i + 1}")
         torch.cuda.synchronize()
-        dog.kick(f"warm-up step {i + 1}")
+        if i > 0 or args.warmup == 1:
+            dog.set_step_time(time.time() - t0)
     barrier()
-    dog.kick("timed region")
+    dog.mark("warm-up")
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -194,12 +252,13 @@ def _run(args, ref_path) -> None:
     ev0.record()
     for i in range(args.steps):
         loss = step(dev_ids[i % 2], dev_lbl[i % 2])
+        dog.mark(f"timed step {i + 1}")
     ev1.record()
     barrier()
     ms_total = reduce(ev0.elapsed_time(ev1), dist.ReduceOp.MAX)
-    dog.kick("end-to-end region")
     clocks = sampler.stop() if rank == 0 else None
-    final_loss = float(loss.item()) if loss is not None else None
+    # the loss lives on the rank that holds the last stage; every rank learns it so that rank 0 can print it
+    final_loss = reduce(float(loss.item()) if loss is not None else float("-inf"), dist.ReduceOp.MAX)
 
     e2e = None
     if not args.no_e2e:
@@ -219,6 +278,7 @@ def _run(args, ref_path) -> None:
             if l is not None:
                 hl = l.float().cpu()
                 d2h += hl.numel() * hl.element_size()
+            dog.mark(f"end-to-end step {i + 1}")
         e1.record()
         barrier()
         e2e_ms = reduce(e0.elapsed_time(e1), dist.ReduceOp.MAX)
@@ -236,6 +296,7 @@ def _run(args, ref_path) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (uniform token ids, labels shifted by one; random-init weights)", "impl": "reference",
+            "reference_system": system,
             "config": {"model": desc, "global_batch": args.batch, "seq_len": args.seq, "microbatches": n_mb,
                        "parallelism": f"pp{world}" + (f"x{virtual}v" if virtual > 1 else ""), "schedule": sched_name,
                        "optimizer": "torch.optim.AdamW(fused=True) lr 3e-4",

@@ -46,7 +46,6 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sm-reserve", type=int, default=None,
                     help="SMs kept out of the GEMM grid for communication kernels (default: 0 on 1 GPU, 8 otherwise)")
-    ap.add_argument("--timing", action="store_true", help="also report the measured bubble of the last step")
     return ap.parse_args()
 
 
@@ -158,7 +157,7 @@ def main() -> None:
         virtual = 1
     pipe = build_llama_pipeline(
         cfg, args.batch, args.seq, args.microbatches, device, schedule=schedule, virtual_stages=virtual,
-        lr=3e-4, weight_decay=0.1, record_timing=args.timing,
+        lr=3e-4, weight_decay=0.1,
     )
 
     # synthetic data of the named shape: uniform token ids, labels = ids shifted by one
@@ -215,15 +214,8 @@ def main() -> None:
     launches = sum_over_ranks(float(_lib.launch_count() - launches0))
     clocks = sampler.stop() if rank == 0 else None
     _lib.check_device_errors()
-    final_loss = float(loss.item()) if loss is not None else None
-    bubble = None
-    if args.timing and pipe.schedule.last_step_stats is not None:
-        bubble = max_over_ranks(pipe.schedule.last_step_stats["bubble"])
-        dump_dir = os.environ.get("PIPPY_TIMELINE_DIR")
-        if dump_dir:
-            os.makedirs(dump_dir, exist_ok=True)
-            with open(os.path.join(dump_dir, f"timeline_rank{rank}.json"), "w") as f:
-                json.dump(pipe.schedule.last_step_stats, f)
+    # the loss lives on the rank that holds the last stage; every rank learns it so that rank 0 can print it
+    final_loss = max_over_ranks(float(loss.item()) if loss is not None else float("-inf"))
 
     # ---------------------------------------------------------------- end-to-end region (H2D inputs + D2H loss each step)
     e2e = None
@@ -255,6 +247,49 @@ def main() -> None:
             "d2h_bytes_per_step": int(sum_over_ranks(float(d2h)) / args.steps),
             "ms_per_step": e2e_ms / args.steps,
         }
+        _lib.check_device_errors()
+
+    # ---------------------------------------------------------------- one more step with per-action CUDA events
+    # (outside both timed regions: the events cost a few hundred host calls per step)
+    pipe.schedule.record_timing = True
+    barrier()
+    pipe.train_step(dev_ids[0], dev_lbl[0])
+    barrier()
+    pipe.schedule.record_timing = False
+    stats = pipe.schedule.last_step_stats
+    bubble = max_over_ranks(stats["bubble"])
+    per_op = {k: max_over_ranks(stats["per_op_s"].get(k, 0.0)) for k in ("F", "B", "I", "W")}
+    busy_min = -max_over_ranks(-stats["busy_s"])
+    busy_max = max_over_ranks(stats["busy_s"])
+    dump_dir = os.environ.get("PIPPY_TIMELINE_DIR")
+    if dump_dir:
+        os.makedirs(dump_dir, exist_ok=True)
+        with open(os.path.join(dump_dir, f"timeline_rank{rank}.json"), "w") as f:
+            json.dump(stats, f)
+
+    # ---------------------------------------------------------------- same stages under interleaved 1F1B (the
+    # schedule the reference arm runs), so that the runtime's and the schedule's share of a gain can be told apart
+    like_for_like = None
+    if world > 1 and schedule != "interleaved_1f1b" and args.microbatches % world == 0 and virtual > 1 \
+            and schedule != "zbv":
+        from pippy_b200.models.llama import causal_lm_loss
+        from pippy_b200.schedules import ScheduleInterleaved1F1B
+
+        main_schedule = pipe.schedule
+        pipe.schedule = ScheduleInterleaved1F1B(pipe.stages, args.microbatches, loss_fn=causal_lm_loss)
+        n_il = max(1, min(args.steps, 3))
+        pipe.train_step(dev_ids[0], dev_lbl[0])  # builds the action list, untimed
+        barrier()
+        i0, i1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        i0.record()
+        for i in range(n_il):
+            pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
+        i1.record()
+        barrier()
+        il_ms = max_over_ranks(i0.elapsed_time(i1))
+        like_for_like = {"value": args.batch * args.seq * n_il / (il_ms * 1e-3), "unit": "tokens/s",
+                         "ms_per_step": il_ms / n_il, "steps": n_il}
+        pipe.schedule = main_schedule
         _lib.check_device_errors()
 
     peak_mem = max_over_ranks(torch.cuda.max_memory_allocated() / 2**30)
@@ -295,8 +330,11 @@ def main() -> None:
             "gpu_launches": int(launches),
             "peak_mem_gb_max_rank": peak_mem,
         }
-        if bubble is not None:
-            out["bubble_measured"] = bubble
+        out["bubble_measured"] = bubble
+        out["per_op_s_max_rank"] = per_op
+        out["busy_s_min_max_rank"] = [busy_min, busy_max]
+        if like_for_like is not None:
+            out["interleaved_1f1b"] = like_for_like
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

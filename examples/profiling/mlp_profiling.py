@@ -1,9 +1,11 @@
 """torch.profiler chrome traces per rank plus the schedule's own per-action timing and bubble
 (reference examples/profiling/mlp_profiling.py).
 
-    torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 2 examples/profiling/mlp_profiling.py
+    torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 2 examples/profiling/mlp_profiling.py --out traces
 """
+import argparse
 import os
+import tempfile
 
 import torch
 import torch.distributed as dist
@@ -13,6 +15,10 @@ import pippy_b200 as pp
 from pippy_b200.models.mlp import ReadmeMLP
 
 if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=os.environ.get("TRACE_DIR"),
+                    help="directory for the trace files (default: a fresh directory under the system temp dir)")
+    args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
     torch.manual_seed(0)
@@ -28,7 +34,13 @@ if __name__ == "__main__":
                 schedule.step(target=target, losses=[])
             else:
                 schedule.step()
-    out = os.environ.get("TRACE_DIR", ".")
+    out = args.out
+    if out is None:
+        # every rank must write into the same directory: rank 0 makes it and tells the others
+        box = [tempfile.mkdtemp(prefix="pippy_b200_traces_") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        out = box[0]
+    os.makedirs(out, exist_ok=True)
     prof.export_chrome_trace(os.path.join(out, f"pipeline_rank{rank}.json"))
     stats = schedule.last_step_stats
     print(f"rank {rank}: bubble {stats['bubble']:.3f}, per-op seconds {stats['per_op_s']}")
@@ -36,5 +48,7 @@ if __name__ == "__main__":
     from pippy_b200.schedules import gather_measured_trace
 
     gather_measured_trace(schedule, os.path.join(out, "pipeline_schedule.json"))
+    if rank == 0:
+        print(f"traces written to {out}")
     dist.barrier()
     dist.destroy_process_group()

@@ -150,16 +150,26 @@ def _match_checkpoint_name(name: str, weight_map: Dict[str, str]) -> Optional[st
 
 
 def _set_tensor(module: nn.Module, name: str, value: torch.Tensor, device, dtype) -> None:
+    """Installs ``value`` as parameter/buffer ``name``.  With ``dtype=None`` a floating-point value takes the dtype
+    of the tensor it replaces (reference utilities/hf_checkpoint.py:244-324: an fp32 shard loaded into a bf16 stage
+    stays bf16; integer and bool tensors are never cast).  When shape, dtype and device already match, the value is
+    copied into the existing storage, so a parameter that lives in a flat buffer (``optim.FlatParams``) stays
+    there; only meta tensors and genuine layout changes replace the object."""
     *path, leaf = name.split(".")
     mod = module
     for atom in path:
         mod = getattr(mod, atom)
-    if dtype is not None and value.is_floating_point():
-        value = value.to(dtype)
+    is_param = leaf in mod._parameters and mod._parameters[leaf] is not None
+    old = mod._parameters[leaf] if is_param else mod._buffers.get(leaf)
+    if value.is_floating_point():
+        want = dtype if dtype is not None else (old.dtype if old is not None and old.is_floating_point() else None)
+        if want is not None:
+            value = value.to(want)
     if device is not None:
         value = value.to(device)
-    if leaf in mod._parameters and mod._parameters[leaf] is not None:
-        old = mod._parameters[leaf]
+    elif old is not None and not old.is_meta:
+        value = value.to(old.device)
+    if is_param:
         if old.is_meta or old.shape != value.shape or old.device != value.device or old.dtype != value.dtype:
             new = nn.Parameter(value, requires_grad=old.requires_grad)
             for attr in ("main_grad",):
@@ -170,8 +180,7 @@ def _set_tensor(module: nn.Module, name: str, value: torch.Tensor, device, dtype
             with torch.no_grad():
                 old.copy_(value)
     elif leaf in mod._buffers:
-        old = mod._buffers[leaf]
-        if old is None or old.is_meta or old.shape != value.shape:
+        if old is None or old.is_meta or old.shape != value.shape or old.dtype != value.dtype:
             mod._buffers[leaf] = value
         else:
             old.copy_(value)
@@ -183,7 +192,8 @@ def load_checkpoint(model: nn.Module, index_filename: str, optim=None, device=No
                     checkpoint_prefix: Optional[str] = None, group: Optional[dist.ProcessGroup] = None,
                     strict: bool = True):
     """Loads the tensors ``model`` (a stage module, a stage, or the whole model) needs from a sharded checkpoint.
-    ``checkpoint_prefix`` is prepended to the module's names when looking them up. Returns ``model``."""
+    ``checkpoint_prefix`` is prepended to the module's names when looking them up. Returns ``model``, or
+    ``(model, optim)`` when an optimizer was passed (reference utilities/hf_checkpoint.py:66-146)."""
     module = model.submod if hasattr(model, "submod") else model
     with open(index_filename) as f:
         index = json.load(f)
@@ -216,4 +226,5 @@ def load_checkpoint(model: nn.Module, index_filename: str, optim=None, device=No
         path = os.path.join(ckpt_dir, _optim_file(rank, world))
         if os.path.exists(path):
             optim.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
+        return model, optim
     return model

@@ -120,6 +120,12 @@ long long pb_launch_count() { return g_launch_count; }
 void pb_launch_count_reset() { g_launch_count = 0; }
 void pb_count_launch(int n) { g_launch_count += n; }
 
+// Limit of the peer-flag waits in SM cycles (about 3 s by default: a peer may lag by a whole schedule action).
+static long long g_peer_wait_cycles = 6000000000LL;
+long long pb_peer_wait_cycles() { return g_peer_wait_cycles; }
+// `ms` milliseconds at a nominal 2 GHz SM clock; a lower clock only makes the wait longer.  ms <= 0 restores the default.
+void pb_set_peer_wait_ms(double ms) { g_peer_wait_cycles = ms > 0 ? (long long)(ms * 2.0e6) : 6000000000LL; }
+
 int pb_device_sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;

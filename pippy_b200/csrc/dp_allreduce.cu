@@ -1,14 +1,21 @@
 // Data-parallel gradient all-reduce fused with the cast and the 1/(microbatches * replicas) scale, over NVLink
-// peer memory (one kernel, no NCCL):
+// peer memory (one kernel, no NCCL).  Rank r owns slice r of the bucket.
 //
-//   phase 0  every rank casts its fp32 gradient bucket * scale to bf16 into its staging buffer (the wire format)
-//   phase 1  rank r owns slice r of the bucket: it loads that slice from every peer's staging buffer (P2P loads),
-//            adds its own fp32 values, writes the fp32 sum into its own gradient buffer and stores the bf16 sum
-//            into every peer's staging buffer (P2P stores)
-//   phase 2  every rank converts the slices it does not own from staging back to fp32
+//   pass A   every rank casts the slices it does NOT own (fp32 gradient * scale -> bf16) into its staging buffer,
+//            the wire format its peers will read.  Its own slice is never cast: pass B reads it in fp32.
+//   pass B   the owner of a slice loads that slice from every peer's staging buffer (P2P loads), adds its own fp32
+//            values, rounds the sum to bf16 ONCE, stores that bf16 sum into every peer's staging buffer (P2P
+//            stores, over the values it has just read) and writes the same rounded value, widened to fp32, into
+//            its own gradient buffer.  Every replica therefore ends with bit-identical gradients.
+//   pass C   every rank widens the slices it does not own from staging back to fp32.
+//
+// Each gradient element is read and written twice locally (three times in a cast-everything-first design) and
+// crosses NVLink once in each direction as bf16.
 //
 // Ranks synchronise with epoch-numbered flags in each other's memory (st.release.sys / ld.acquire.sys, bounded
-// waits); CTAs of one GPU synchronise with a counter barrier (the grid is sized to be co-resident).
+// waits).  Inside one GPU there is no grid barrier: the last CTA to finish a pass (an arrival counter) publishes
+// the flag, and every CTA waits for the peers' flags on its own, so the kernel makes progress even when some of its
+// CTAs only become resident after others have finished (it shares the GPU with persistent GEMM kernels).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -24,18 +31,19 @@ using namespace pbp;
 constexpr int MAX_RANKS = 8;
 constexpr int THREADS = 512;
 constexpr int UNROLL = 4;  // independent 8-element groups per thread and loop trip: the passes are latency-bound otherwise
+constexpr int ERR_PEER = 3;
 
 struct Params {
   float* grad;                        // local fp32 gradients [n]
   __nv_bfloat16* staging[MAX_RANKS];  // every rank's staging buffer [n] (index = rank; own included)
   int* flags[MAX_RANKS];              // every rank's flag block: [0..W) ready, [W..2W) done
-  int* local_counter;                 // grid barrier counter (local)
+  int* local_counter;                 // two arrival counters (local), one per pass; zeroed before every launch
   int* err;
   long long n;
+  long long wait_cycles;
   float scale;
   int rank, world;
   int epoch;          // grows by 1 per call
-  int barrier_base;   // local_counter value before this call
 };
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
@@ -55,49 +63,71 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return u;
 }
 
+// The CTA's writes become visible system-wide, then it counts itself in; the CTA that completes the count
+// publishes `epoch` at flags[q][slot] of every rank q.
+__device__ __forceinline__ void arrive_and_publish(const Params& p, int* counter, int slot_base) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = (atomicAdd(counter, 1) + 1 == (int)gridDim.x) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + slot_base + p.rank, p.epoch);
+  }
+}
+
+// Every CTA waits until all ranks have published `epoch` in this rank's flag block.
+__device__ __forceinline__ bool wait_all_ranks(const Params& p, int slot_base) {
+  bool ok = true;
+  if (threadIdx.x < p.world)
+    ok = wait_flag_sys(p.flags[p.rank] + slot_base + threadIdx.x, p.epoch, p.err, ERR_PEER, p.wait_cycles);
+  return __syncthreads_and(ok);
+}
+
 __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
   const long long nvec = p.n / 8;  // 8 elements per 16-byte bf16 vector
   const long long tid = blockIdx.x * (long long)THREADS + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * THREADS;
   const int W = p.world;
   __nv_bfloat16* my_stage = p.staging[p.rank];
-  int bar = p.barrier_base;
+  const long long per = (nvec + W - 1) / W;
+  const long long lo = per * p.rank < nvec ? per * p.rank : nvec;
+  const long long hi = (lo + per < nvec) ? lo + per : nvec;
+  const long long n_other = nvec - (hi - lo);
+  // position j in [0, n_other) of the vectors this rank does not own -> vector index
+  auto other = [&](long long j) { return j < lo ? j : j + (hi - lo); };
 
-  // ---- phase 0: cast + scale into the wire buffer
-  for (long long i0 = tid; i0 < nvec; i0 += nthreads * UNROLL) {
+  // ---- pass A: cast + scale the slices the peers will read
+  for (long long j0 = tid; j0 < n_other; j0 += nthreads * UNROLL) {
     float4 a[UNROLL], b[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const long long i = i0 + u * nthreads;
-      if (i < nvec) {
+      const long long j = j0 + u * nthreads;
+      if (j < n_other) {
+        const long long i = other(j);
         a[u] = reinterpret_cast<const float4*>(p.grad)[2 * i];
         b[u] = reinterpret_cast<const float4*>(p.grad)[2 * i + 1];
       }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const long long i = i0 + u * nthreads;
-      if (i >= nvec) continue;
+      const long long j = j0 + u * nthreads;
+      if (j >= n_other) continue;
       float f[8] = {a[u].x * p.scale, a[u].y * p.scale, a[u].z * p.scale, a[u].w * p.scale,
                     b[u].x * p.scale, b[u].y * p.scale, b[u].z * p.scale, b[u].w * p.scale};
-      reinterpret_cast<uint4*>(my_stage)[i] = pack8(f);
+      reinterpret_cast<uint4*>(my_stage)[other(j)] = pack8(f);
     }
   }
-  __threadfence_system();
-  bar += gridDim.x;
-  if (!grid_barrier(p.local_counter, bar, p.err, 3)) return;
-  if (blockIdx.x == 0 && threadIdx.x < W) st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);  // "ready"
-  bool ok = true;
-  if (threadIdx.x < W) ok = wait_flag_sys(p.flags[p.rank] + threadIdx.x, p.epoch, p.err, 3);
-  if (!__syncthreads_and(ok)) return;
+  arrive_and_publish(p, p.local_counter, 0);  // "ready"
+  if (!wait_all_ranks(p, 0)) return;
 
-  // ---- phase 1: reduce the slice this rank owns, publish the sum to everyone
-  const long long per = (nvec + W - 1) / W;
-  const long long lo = per * p.rank;
-  const long long hi = (lo + per < nvec) ? lo + per : nvec;
+  // ---- pass B: reduce the slice this rank owns, publish the rounded sum to everyone
   for (long long i0 = lo + tid; i0 < hi; i0 += nthreads * UNROLL) {
     float acc[UNROLL][8];
-    // own fp32 values and, peer by peer, UNROLL remote vectors in flight at once (a peer load takes microseconds)
     {
       float4 a[UNROLL], b[UNROLL];
 #pragma unroll
@@ -117,6 +147,7 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
         acc[u][6] = b[u].z * p.scale; acc[u][7] = b[u].w * p.scale;
       }
     }
+    // peer by peer, UNROLL remote vectors in flight at once (a peer load takes microseconds)
     for (int q = 1; q < W; ++q) {
       const uint4* src = reinterpret_cast<const uint4*>(p.staging[(p.rank + q) % W]);
       uint4 v[UNROLL];
@@ -137,32 +168,30 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
     for (int u = 0; u < UNROLL; ++u) {
       const long long i = i0 + u * nthreads;
       if (i >= hi) continue;
-      reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
-      reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
       const uint4 packed = pack8(acc[u]);
+      float r[8];
+      unpack8(packed, r);  // what the peers will hold
+      reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(r[0], r[1], r[2], r[3]);
+      reinterpret_cast<float4*>(p.grad)[2 * i + 1] = make_float4(r[4], r[5], r[6], r[7]);
       for (int q = 1; q < W; ++q) reinterpret_cast<uint4*>(p.staging[(p.rank + q) % W])[i] = packed;
     }
   }
-  __threadfence_system();
-  bar += gridDim.x;
-  if (!grid_barrier(p.local_counter, bar, p.err, 3)) return;
-  if (blockIdx.x == 0 && threadIdx.x < W) st_release_sys(p.flags[threadIdx.x] + W + p.rank, p.epoch);  // "done"
-  ok = true;
-  if (threadIdx.x < W) ok = wait_flag_sys(p.flags[p.rank] + W + threadIdx.x, p.epoch, p.err, 3);
-  if (!__syncthreads_and(ok)) return;
+  arrive_and_publish(p, p.local_counter + 1, W);  // "done"
+  if (!wait_all_ranks(p, W)) return;
 
-  // ---- phase 2: slices owned by the others are now complete in my staging buffer
-  for (long long i0 = tid; i0 < nvec; i0 += nthreads * UNROLL) {
+  // ---- pass C: slices owned by the others are now complete in my staging buffer
+  for (long long j0 = tid; j0 < n_other; j0 += nthreads * UNROLL) {
     uint4 v[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const long long i = i0 + u * nthreads;
-      if (i < nvec && !(i >= lo && i < hi)) v[u] = reinterpret_cast<const uint4*>(my_stage)[i];
+      const long long j = j0 + u * nthreads;
+      if (j < n_other) v[u] = reinterpret_cast<const uint4*>(my_stage)[other(j)];
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const long long i = i0 + u * nthreads;
-      if (i >= nvec || (i >= lo && i < hi)) continue;
+      const long long j = j0 + u * nthreads;
+      if (j >= n_other) continue;
+      const long long i = other(j);
       float f[8];
       unpack8(v[u], f);
       reinterpret_cast<float4*>(p.grad)[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
@@ -176,12 +205,14 @@ __global__ void __launch_bounds__(THREADS) dp_allreduce_kernel(Params p) {
 extern "C" {
 
 // grad: local fp32 [n] (n % 8 == 0). staging/flags: arrays of `world` device pointers (this rank's own included) to
-// bf16[n] and int[2*world] peer-mapped buffers. counter: local int (zero-initialised once); the caller passes its
-// current value in `barrier_base` and adds 2 * grid (returned through *grid_out) afterwards.
+// bf16[n] and int[2*world] peer-mapped buffers. counter: two local ints, cleared here on the stream before the
+// launch (so a call that gave up half way cannot disturb the next one).  `epoch` must grow from call to call.  A
+// peer that never arrives makes the waits run out after pb_peer_wait_cycles(): the kernel then returns with the
+// device error word set to 3 and the gradients of this call undefined; the context stays usable.
 int pb_dp_allreduce(float* grad, void** staging, int** flags, int* counter, int* err, long long n, float scale,
-                    int rank, int world, int epoch, int barrier_base, int max_ctas, int* grid_out, void* stream_) {
+                    int rank, int world, int epoch, int max_ctas, int* grid_out, void* stream_) {
   using namespace pbd;
-  if (world < 1 || world > MAX_RANKS || n % 8 != 0) return -1;
+  if (world < 1 || world > MAX_RANKS || n % 8 != 0 || rank < 0 || rank >= world) return -1;
   Params p;
   p.grad = grad;
   for (int i = 0; i < world; ++i) {
@@ -191,16 +222,18 @@ int pb_dp_allreduce(float* grad, void** staging, int** flags, int* counter, int*
   p.local_counter = counter;
   p.err = err;
   p.n = n;
+  p.wait_cycles = pb_peer_wait_cycles();
   p.scale = scale;
   p.rank = rank;
   p.world = world;
   p.epoch = epoch;
-  p.barrier_base = barrier_base;
-  long long want = (n / 8 + THREADS - 1) / THREADS;
+  long long want = (n / 8 + (long long)THREADS * UNROLL - 1) / ((long long)THREADS * UNROLL);
   int grid = (int)(want < max_ctas ? want : max_ctas);
   if (grid < 1) grid = 1;
   *grid_out = grid;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  cudaError_t e = cudaMemsetAsync(counter, 0, 2 * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
   dp_allreduce_kernel<<<grid, THREADS, 0, stream>>>(p);
   pb_count_launch(1);
   return (int)cudaGetLastError();

@@ -363,13 +363,20 @@ def flash_backward(do, q, k, v, o, lse, B, S, Hq, Hkv, D, scale, causal=True, dq
 
 
 class _RopeAttentionFn(torch.autograd.Function):
-    """qkv [B*S, (Hq + 2 Hkv) * D] -> attention output [B*S, Hq * D]; RoPE is applied to q and k in place."""
+    """qkv [B*S, (Hq + 2 Hkv) * D] -> attention output [B*S, Hq * D].
+
+    RoPE is applied to the q and k columns of ``qkv`` IN PLACE (the rotated projection is what the backward needs,
+    and a second copy of the largest activation of the layer would be kept for nothing).  The kernel writes through
+    a raw pointer, so the tensor's version counter is bumped by hand: a producer that had saved ``qkv`` for its own
+    backward gets autograd's usual "modified by an inplace operation" error instead of silently wrong gradients.
+    The gradient returned for ``qkv`` is with respect to its value BEFORE the rotation."""
 
     @staticmethod
     def forward(ctx, qkv, cos, sin, B, S, Hq, Hkv, D, scale, causal):
         T = B * S
         if cos is not None:
             _rope_inplace(qkv, cos, sin, T, S, Hq + Hkv, D, 1.0)
+            torch.autograd.graph.increment_version(qkv)
         q = qkv[:, : Hq * D]
         k = qkv[:, Hq * D : (Hq + Hkv) * D]
         v = qkv[:, (Hq + Hkv) * D :]
@@ -396,7 +403,11 @@ class _RopeAttentionFn(torch.autograd.Function):
 def rope_attention(qkv, cos, sin, B: int, S: int, Hq: int, Hkv: int, D: int, scale: Optional[float] = None,
                    causal: bool = True):
     """Causal self-attention over a packed projection ``qkv`` of shape ``[B*S, (Hq + 2*Hkv) * D]``
-    (q heads, then k heads, then v heads), with rotary embedding of q and k when ``cos``/``sin`` are given."""
+    (q heads, then k heads, then v heads), with rotary embedding of q and k when ``cos``/``sin`` are given.
+
+    On the kernel path (CUDA bf16) the rotation overwrites the q and k columns of ``qkv``: the caller's tensor holds
+    the rotated projection afterwards (its version counter is bumped).  Pass a clone to keep the original.  The
+    CPU path leaves ``qkv`` untouched."""
     scale = (1.0 / math.sqrt(D)) if scale is None else scale
     if _use_kernels(qkv):
         return _RopeAttentionFn.apply(qkv, cos, sin, B, S, Hq, Hkv, D, scale, causal)

@@ -132,6 +132,10 @@ class FusedAdamW:
 
     def load_state_dict(self, sd) -> None:
         self.step_count = sd["step"]
+        self.lr = sd.get("lr", self.lr)
+        self.betas = tuple(sd.get("betas", self.betas))
+        self.eps = sd.get("eps", self.eps)
+        self.weight_decay = sd.get("weight_decay", self.weight_decay)
         for dst, src in zip(self.m, sd["m"]):
             dst.copy_(src)
         for dst, src in zip(self.v, sd["v"]):

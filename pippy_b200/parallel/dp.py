@@ -23,7 +23,7 @@ from ..optim import FlatParams
 
 
 class GradReducer:
-    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 64,
+    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 96,
                  average: bool = True):
         self.flat = flat
         self.group = dp_group
@@ -32,7 +32,6 @@ class GradReducer:
         self.scale = (1.0 / self.world) if average else 1.0
         self.max_ctas = max_ctas
         self.epoch = 0
-        self.barrier_base = 0
         self._ranges: Dict[int, Tuple[int, int]] = {}
         self.fused = (
             flat.grad.is_cuda and flat.grad.dtype == torch.float32 and self.world > 1 and self.world <= 8
@@ -46,7 +45,7 @@ class GradReducer:
             self.n_padded = n
             self.staging = SymmetricBuffer(n * 2, dp_group, flat.grad.device)
             self.flags = SymmetricBuffer(4096, dp_group, flat.grad.device)
-            self.counter = torch.zeros(1, dtype=torch.int32, device=flat.grad.device)
+            self.counter = torch.zeros(2, dtype=torch.int32, device=flat.grad.device)
             self._stream = torch.cuda.Stream(device=flat.grad.device)
 
     def _stage_range(self, stage) -> Tuple[int, int]:
@@ -101,11 +100,10 @@ class GradReducer:
             rc = _lib.lib().pb_dp_allreduce(
                 ctypes.c_void_p(grad.data_ptr() + lo * 4), stag, flg, _lib.ptr(self.counter),
                 _lib.ptr(_lib.err_word(grad.device)), _lib.c_ll(n), _lib.c_float(self.scale), _lib.c_int(self.rank),
-                _lib.c_int(self.world), _lib.c_int(self.epoch), _lib.c_int(self.barrier_base),
+                _lib.c_int(self.world), _lib.c_int(self.epoch),
                 _lib.c_int(self.max_ctas), ctypes.byref(grid), ctypes.c_void_p(self._stream.cuda_stream),
             )
             _lib.check(rc, "pb_dp_allreduce")
-            self.barrier_base += 2 * grid.value
             done = torch.cuda.Event()
             done.record(self._stream)
             self._pending.append(done)

@@ -13,8 +13,16 @@ import torch.distributed as dist
 
 
 def _grad_of(p: torch.nn.Parameter) -> Optional[torch.Tensor]:
+    """The gradient to reduce.  A parameter that lives in a flat buffer has ``main_grad``; ops outside this
+    package's kernels (and every op on the CPU path) still leave their share in ``.grad``, so that is folded into
+    ``main_grad`` first: otherwise the reduction would sum zeros and the copies would drift apart."""
     mg = getattr(p, "main_grad", None)
-    return mg if mg is not None else p.grad
+    if mg is None:
+        return p.grad
+    if p.grad is not None:
+        mg.add_(p.grad.to(mg.dtype))
+        p.grad = None
+    return mg
 
 
 def _get(module, qualname: str):

@@ -133,6 +133,7 @@ class PipelineSchedule:
         p2p_timeout_s: Optional[float] = None,
         record_timing: bool = False,
         use_link_groups: bool = True,
+        return_outputs: bool = True,
     ):
         self._stages = sorted(stages, key=lambda s: s.stage_index)
         self._stage_by_index = {s.stage_index: s for s in self._stages}
@@ -145,6 +146,10 @@ class PipelineSchedule:
         self.grad_reducer = grad_reducer
         self.p2p_timeout_s = p2p_timeout_s
         self.record_timing = record_timing
+        # A training loop that only wants the losses passes False: the last stage then neither keeps every
+        # microbatch's output alive until the end of the step nor concatenates them (for a language model that is
+        # the full [batch, seq, vocab] logits, twice).
+        self.return_outputs = return_outputs
         self.last_step_stats: Optional[Dict[str, Any]] = None
         first = self._stages[0]
         self.pp_group_size = first.group_size
@@ -158,6 +163,7 @@ class PipelineSchedule:
         )
         for st in self._stages:
             st.has_backward = self._has_backward
+            st.keep_outputs = return_outputs
             st._prepare_forward_infra(n_microbatches)
         self.link_groups = None
         if dist.is_available() and dist.is_initialized() and self.pp_group_size > 1 and use_link_groups:
@@ -363,11 +369,13 @@ class PipelineSchedule:
                 raise RuntimeError(f"unknown action {action}")
 
         self._wait(send_works, Action(self._stages[0].stage_index, Op.SEND_F))
+        # the reducer's kernels run on a side stream over the same flat gradient buffer: this stream must wait for
+        # them before anything else (the scaling below, the optimizer) touches the gradients
+        if self.grad_reducer is not None and self._has_backward:
+            self.grad_reducer.finish()
         if self.scale_grads and self._has_backward:
             for st in self._stages:
                 st.scale_grads(self._n_microbatches)
-        if self.grad_reducer is not None and self._has_backward:
-            self.grad_reducer.finish()
         if timer:
             timer.end_step()
             self.last_step_stats = timer.summary()
@@ -384,12 +392,15 @@ class PipelineSchedule:
         for st in self._stages:
             st.clear_runtime_states()
             st.has_backward = self._has_backward
+            st.keep_outputs = self.return_outputs
         args_split, kwargs_split = self._split_inputs(args, kwargs)
         if target is not None:
             targets_split = list(torch.tensor_split(target, self._n_microbatches))
         else:
             targets_split = None
         self._step_microbatches(args_split, kwargs_split, targets_split, losses)
+        if not self.return_outputs:
+            return None
         for st in self._stages:
             if st.is_last:
                 chunks = [st.output_chunks[mb] for mb in range(self._n_microbatches)]

@@ -108,6 +108,7 @@ class PipelineStageBase:
         self.output_dests: Dict[int, List[int]] = {}  # output idx -> consumer stages
         self.chunks: Optional[int] = None
         self.has_backward = False
+        self.keep_outputs = True  # the schedule clears this when its caller does not want the merged output
         self.scale_grads_by: Optional[float] = None
 
         # run-time state
@@ -243,7 +244,9 @@ class PipelineStageBase:
     def get_fwd_send_ops(self, mb: Optional[int] = None) -> List[dist.P2POp]:
         """isend ops for every (output, remote consumer stage) of microbatch ``mb``, consumers ascending."""
         mb = (self.fwd_chunk_id - 1) if mb is None else mb
-        outputs = self._sent_outputs[mb]
+        outputs = getattr(self, "_sent_outputs", {}).get(mb)
+        if outputs is None:
+            return []
         ops: List[Tuple[int, int, dist.P2POp]] = []
         for out_idx, consumers in self.output_dests.items():
             out = outputs[out_idx]
@@ -368,7 +371,7 @@ class PipelineStageBase:
         def _detached(o):
             return o.detach() if isinstance(o, torch.Tensor) else o
 
-        if self.is_last:
+        if self.is_last and self.keep_outputs:
             self.output_chunks[mb] = (
                 tuple(_detached(o) for o in output) if isinstance(output, tuple) else _detached(output)
             )
@@ -376,7 +379,8 @@ class PipelineStageBase:
         self.fwd_cache[mb] = (output_tuple, flat_inputs)
         if not hasattr(self, "_sent_outputs"):
             self._sent_outputs: Dict[int, Tuple[Any, ...]] = {}
-        self._sent_outputs[mb] = tuple(_detached(o) for o in output_tuple)
+        if any(self.output_dests.values()):  # the last stage sends nothing: do not pin its outputs
+            self._sent_outputs[mb] = tuple(_detached(o) for o in output_tuple)
         self.fwd_chunk_id = mb + 1
         logger.debug("[%d] Forwarded chunk %d, outputs: %s", self.stage_index, mb, map_debug_info(output))
         return output

@@ -131,7 +131,7 @@ def build_llama_pipeline(
             grad_reducer = GradReducer(flat, dp_group)
     cls = SCHEDULES[schedule]
     kw = dict(schedule_kwargs or {})
-    kw.update(loss_fn=causal_lm_loss, grad_reducer=grad_reducer, record_timing=record_timing)
+    kw.update(loss_fn=causal_lm_loss, grad_reducer=grad_reducer, record_timing=record_timing, return_outputs=False)
     if schedule in ("gpipe", "1f1b"):
         if virtual_stages != 1:
             raise ValueError(f"schedule {schedule!r} runs one stage per rank")
@@ -213,7 +213,7 @@ def build_gpt2_pipeline(
 
         reducer = GradReducer(flat, dp_group)
     cls = SCHEDULES[schedule]
-    kw = dict(loss_fn=gpt2_loss(cfg), grad_reducer=reducer, record_timing=record_timing)
+    kw = dict(loss_fn=gpt2_loss(cfg), grad_reducer=reducer, record_timing=record_timing, return_outputs=False)
     sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat, n_microbatches, holds_first=(pp_rank == 0),
                     holds_last=(last_rank == pp_rank), tied=tied)
@@ -275,7 +275,7 @@ def build_mixtral_pipeline(
 
         reducer = GradReducer(flat_dense, ep_group)
     cls = SCHEDULES[schedule]
-    kw = dict(loss_fn=causal_lm_loss, grad_reducer=reducer, record_timing=record_timing)
+    kw = dict(loss_fn=causal_lm_loss, grad_reducer=reducer, record_timing=record_timing, return_outputs=False)
     sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat_dense, n_microbatches, holds_first=(pp_rank == 0),
                     holds_last=((num_stages - 1) % pp_size == pp_rank))

@@ -7,7 +7,7 @@ import torch
 from _mp import run_ranks
 
 
-def _pp_dp(rank, world, schedule):
+def _pp_dp(rank, world, schedule, scale_grads=False):
     import torch.distributed as dist
 
     from pippy_b200.models.gpt2 import GPT2Config
@@ -21,6 +21,8 @@ def _pp_dp(rank, world, schedule):
     v = 1 if schedule == "1f1b" else 2
     pipe = build_gpt2_pipeline(cfg, B, S, n_mb, torch.device("cpu"), schedule=schedule, virtual_stages=v,
                                group=mesh.pp_group, dp_group=mesh.dp_group, dtype=torch.float32, lr=0.0, weight_decay=0.0)
+    # with both a reducer and scale_grads the scaling must come after the reduction has been waited for
+    pipe.schedule.scale_grads = scale_grads
     gen = torch.Generator().manual_seed(100)
     data = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen) for _ in range(2)]  # one batch per replica
     ids = data[mesh.dp_rank]
@@ -64,6 +66,8 @@ def _pp_dp(rank, world, schedule):
             want = total.get((st.stage_index, k))
             if want is None and k == "lm_head.weight":
                 want = total[(0, "wte.weight")]
+            if scale_grads:
+                want = want / n_mb
             torch.testing.assert_close(p.main_grad, want, rtol=2e-4, atol=2e-5, msg=f"{schedule} stage {st.stage_index} {k}")
     dist.barrier()
 
@@ -71,6 +75,10 @@ def _pp_dp(rank, world, schedule):
 @pytest.mark.parametrize("schedule", ["1f1b", "zero_bubble"])
 def test_pp2_dp2_gpt2_tied_weights_and_grad_reduce(schedule):
     run_ranks(_pp_dp, 4, schedule, timeout_s=240)
+
+
+def test_pp2_dp2_grad_reduce_then_scale():
+    run_ranks(_pp_dp, 4, "1f1b", True, timeout_s=240)
 
 
 # ---------------------------------------------------------------------------------------------------------------

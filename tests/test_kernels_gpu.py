@@ -237,3 +237,129 @@ def test_rope_attention_with_rotary():
     assert _rel(out, ref) < 2e-2
     assert _rel(qkv.grad, qf.grad) < 3e-2
 
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+def test_gemm_many_tiles_per_cta(variant, a_mn, b_mn):
+    """4096 x 8192 has 512 tiles of 256 x 256 (2048 of 128 x 128): every persistent CTA works through several
+    tiles, so the accumulator ping-pong in TMEM, the wrap of the shared-memory ring across tiles and the grouped
+    rasterisation all run, as they do in a training step."""
+    from pippy_b200.ops.gemm import gemm
+
+    M, N, K = 4096, 8192, 1024
+    a = _bf16(K, M) if a_mn else _bf16(M, K)
+    b = _bf16(K, N) if b_mn else _bf16(N, K)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    out = gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), variant=variant)
+    assert _rel(out, ref) < 1e-2
+    # a dropped or doubled tile shows as an O(1) error somewhere; rounding alone stays far below this everywhere
+    assert ((out.float() - ref).abs() / ref.abs().clamp(min=8.0)).max().item() < 5e-2
+
+
+def test_gemm_many_tiles_with_reserved_sms():
+    """The grid that leaves SMs free for communication kernels covers the same tiles."""
+    from pippy_b200.ops.gemm import gemm, set_sm_reserve
+
+    M, N, K = 4096, 4096, 512
+    a, b = _bf16(M, K), _bf16(N, K)
+    ref = a.float() @ b.float().t()
+    try:
+        set_sm_reserve(8)
+        out = gemm(a, b)
+    finally:
+        set_sm_reserve(0)
+    assert _rel(out, ref) < 1e-2
+
+
+def test_flash_attention_long_sequence():
+    """The training shape's sequence length: 32 key blocks per query block, head dim 128."""
+    from pippy_b200.ops import functional as pf
+
+    B, S, Hq, Hkv, D = 1, 4096, 2, 2, 128
+    T = B * S
+    qkv = _bf16(T, (Hq + 2 * Hkv) * D).requires_grad_()
+    do = _bf16(T, Hq * D)
+    out = pf.rope_attention(qkv * 1, None, None, B, S, Hq, Hkv, D)
+    out.backward(do)
+    qf = qkv.detach().float().requires_grad_()
+    q = qf[:, : Hq * D].view(B, S, Hq, D)
+    k = qf[:, Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = qf[:, (Hq + Hkv) * D :].view(B, S, Hkv, D)
+    ref = _attn_ref(q, k, v, True, 1 / math.sqrt(D)).reshape(T, Hq * D)
+    ref.backward(do.float())
+    assert _rel(out, ref) < 2e-2
+    g, gr = qkv.grad.float(), qf.grad
+    for name, sl in (("dq", slice(0, Hq * D)), ("dk", slice(Hq * D, (Hq + Hkv) * D)), ("dv", slice((Hq + Hkv) * D, None))):
+        assert _rel(g[:, sl], gr[:, sl]) < 3e-2, name
+
+
+def test_peer_wait_runs_out_and_reports():
+    """Failure detection on the device: the all-reduce kernel is launched as rank 0 of 2 with a second flag block
+    that nobody ever writes (both "ranks" are buffers of this one GPU) and a wait limit of a few milliseconds.
+    The kernel must return by itself, the error word must say "peer wait ran out", and the next launch must work."""
+    import ctypes
+
+    from pippy_b200.ops import _lib
+
+    lib = _lib.lib()
+    lib.pb_set_peer_wait_ms.argtypes = [ctypes.c_double]
+    n = 1 << 16
+    grad = torch.randn(n, device="cuda")
+    staging = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    flags = [torch.zeros(64, device="cuda", dtype=torch.int32) for _ in range(2)]
+    counter = torch.zeros(2, device="cuda", dtype=torch.int32)
+    stag = (ctypes.c_void_p * 2)(*[ctypes.c_void_p(t.data_ptr()) for t in staging])
+    flg = (ctypes.POINTER(ctypes.c_int) * 2)(
+        *[ctypes.cast(ctypes.c_void_p(t.data_ptr()), ctypes.POINTER(ctypes.c_int)) for t in flags])
+    grid = ctypes.c_int(0)
+    err = _lib.err_word(grad.device)
+    try:
+        lib.pb_set_peer_wait_ms(5.0)
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        rc = lib.pb_dp_allreduce(_lib.ptr(grad), stag, flg, _lib.ptr(counter), _lib.ptr(err), _lib.c_ll(n),
+                                 _lib.c_float(0.5), _lib.c_int(0), _lib.c_int(2), _lib.c_int(1), _lib.c_int(8),
+                                 ctypes.byref(grid), _lib.stream_ptr())
+        assert rc == 0
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 1000.0  # gave up after milliseconds, not after the default 3 s
+        with pytest.raises(_lib.KernelError, match="peer wait ran out"):
+            _lib.check_device_errors()
+    finally:
+        lib.pb_set_peer_wait_ms(0.0)
+    # the context is intact: the same kernel as a one-rank group completes and scales the gradients
+    before = grad.clone()
+    rc = lib.pb_dp_allreduce(_lib.ptr(grad), stag, flg, _lib.ptr(counter), _lib.ptr(err), _lib.c_ll(n),
+                             _lib.c_float(0.5), _lib.c_int(0), _lib.c_int(1), _lib.c_int(2), _lib.c_int(8),
+                             ctypes.byref(grid), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    torch.testing.assert_close(grad, (before * 0.5).bfloat16().float())
+
+
+@pytest.mark.parametrize("schedule", ["interleaved_1f1b", "zero_bubble"])
+def test_llama_activation_checkpointing_same_gradients(schedule):
+    """Recomputing each block's forward inside the backward gives the gradients of the plain run: the kernels are
+    deterministic, so everything but the atomically accumulated sums (norm weights, embedding rows) is bit-equal."""
+    from pippy_b200.models.llama import LlamaConfig
+    from pippy_b200.train import build_llama_pipeline
+
+    dev = torch.device("cuda", 0)
+    cfg = LlamaConfig(vocab_size=1024, dim=512, n_layers=4, n_heads=4, ffn_dim=1024)
+    ids = torch.randint(0, cfg.vocab_size, (4, 256), device=dev)
+    grads, losses = {}, {}
+    for ckpt in (False, True):
+        pipe = build_llama_pipeline(cfg, 4, 256, 2, dev, schedule=schedule, virtual_stages=2, seed=11,
+                                    with_optimizer=True, activation_checkpointing=ckpt)
+        pipe.optimizer = None  # keep the accumulated gradients: compare them, not the updated weights
+        losses[ckpt] = float(pipe.train_step(ids, ids))
+        torch.cuda.synchronize()
+        grads[ckpt] = {n: p.main_grad.clone() for st in pipe.stages for n, p in st.submod.named_parameters()}
+    assert abs(losses[True] - losses[False]) < 1e-6
+    for n, g in grads[False].items():
+        assert g.abs().max().item() > 0, n
+        assert _rel(grads[True][n], g) < 1e-3, n

@@ -1,10 +1,15 @@
-"""Fused communication kernels on 2 GPUs (peer memory over NVLink), each against a plain fp32 reference."""
+"""Fused communication kernels on 2 and 4 GPUs (peer memory over NVLink), each against a plain fp32 reference."""
 import pytest
 import torch
 
 from _mp import run_ranks
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
 
 
 def _dp_allreduce(rank, world):
@@ -31,17 +36,19 @@ def _dp_allreduce(rank, world):
         torch.cuda.synchronize()
         _lib.check_device_errors()
         want = sum(per_rank) / world
-        # owned slice is an exact fp32 sum of bf16-rounded peers + own fp32; others come back through bf16
+        # the wire format is bf16: peers' contributions and the published sum are each rounded once
         torch.testing.assert_close(flat.grad.cpu(), want, rtol=2e-2, atol=2e-2)
-        mine = flat.grad.cpu()
         gathered = [torch.empty_like(flat.grad) for _ in range(world)]
         dist.all_gather(gathered, flat.grad)
-        torch.testing.assert_close(gathered[0], gathered[1], rtol=1e-2, atol=1e-2)
+        for other in gathered[1:]:
+            assert torch.equal(gathered[0], other)  # every replica holds the same bits
     dist.barrier()
 
 
-def test_fused_dp_allreduce_two_gpus():
-    run_ranks(_dp_allreduce, 2, backend="nccl", timeout_s=180)
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_dp_allreduce(world):
+    _need(world)
+    run_ranks(_dp_allreduce, world, backend="nccl", timeout_s=180)
 
 
 def _tp_fused(rank, world):
@@ -90,8 +97,10 @@ def _tp_fused(rank, world):
     dist.barrier()
 
 
-def test_fused_tp_linears_two_gpus():
-    run_ranks(_tp_fused, 2, backend="nccl", timeout_s=240)
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_tp_linears(world):
+    _need(world)
+    run_ranks(_tp_fused, world, backend="nccl", timeout_s=240)
 
 
 def _moe_ep(rank, world):
@@ -142,5 +151,7 @@ def _moe_ep(rank, world):
     dist.barrier()
 
 
-def test_expert_parallel_moe_two_gpus():
-    run_ranks(_moe_ep, 2, backend="nccl", timeout_s=240)
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_moe(world):
+    _need(world)
+    run_ranks(_moe_ep, world, backend="nccl", timeout_s=240)
