@@ -57,6 +57,32 @@ struct GemmParams {
   __nv_bfloat16* rs_staging[8];      // mode 2: every rank's staging [world, chunk_rows, N]
   __nv_bfloat16* rs_out;             // mode 2: local result [chunk_rows, N] (row pitch ldc)
   const __nv_bfloat16* rs_residual;  // mode 2: optional [chunk_rows, N] added in the final reduce
+  // ---- grouped modes (0 = plain GEMM): the rows of one operand dimension belong to `n_groups` groups (the
+  // experts of a mixture-of-experts layer) whose sizes are only known on the device.  Group g occupies rows
+  // [group_start[g], group_start[g] + group_rows[g]); every group_start is a multiple of 256.
+  //   1: the M rows of A and C are grouped; each group multiplies its own B: a K-major B is the row-wise stack of
+  //      the groups' [b_group_stride, K] matrices, an MN-major B the stack of their [b_group_stride (= K), N]
+  //      matrices.  Only tiles that hold rows of a group run; output rows of such a tile beyond the group's end
+  //      are written as zeros, so that a later contraction over the rows can run to the next multiple of 64.
+  //   2: the contraction dimension is grouped (both operands MN-major, stored [rows, M] and [rows, N]); group g
+  //      writes (or accumulates into) its own C block at C + g * c_group_stride elements.  The contraction of a
+  //      group runs over whole 64-row blocks: rows between the group's end and the next multiple of 64 must be
+  //      zero in one operand and finite in the other.
+  int grouped;
+  int n_groups;
+  const int* group_rows;
+  const int* group_start;
+  int b_group_stride;
+  long long c_group_stride;
+};
+
+constexpr int MAX_GROUPS = 8;
+
+// Group table in shared memory, built by every CTA from the device-side sizes.
+struct GroupTable {
+  int prefix[MAX_GROUPS + 1];  // mode 1: M tiles before group g
+  int start[MAX_GROUPS];
+  int rows[MAX_GROUPS];
 };
 
 constexpr int BK = 64;
@@ -70,11 +96,11 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.f + t);
 }
 
-__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int num_m_tiles, int& tm, int& tn) {
   const int per_group = p.group_m * p.num_n_tiles;
   const int g = tile / per_group;
   const int first_m = g * p.group_m;
-  const int gsz = min(p.group_m, p.num_m_tiles - first_m);
+  const int gsz = min(p.group_m, num_m_tiles - first_m);
   const int r = tile - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
@@ -117,6 +143,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = bars + 2 * kStages + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  GroupTable* gt = reinterpret_cast<GroupTable*>(smem + kStages * STAGE_BYTES + 152);  // 100 bytes of the 256
+  static_assert((2 * kStages + 4) * 8 + 8 <= 152, "barriers overlap the group table");
   uint8_t* sEpi = smem + kStages * STAGE_BYTES + 256;  // 4 epilogue warps x 32 rows x (128 + 16) bytes
 
   const int warp = threadIdx.x >> 5;
@@ -135,6 +163,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     *abort_flag = 0;
     mbar_fence_init();
+    if (p.grouped) {
+      int acc_tiles = 0;
+      for (int g = 0; g < MAX_GROUPS; ++g) {
+        const int rows = g < p.n_groups ? p.group_rows[g] : 0;
+        gt->prefix[g] = acc_tiles;
+        gt->start[g] = g < p.n_groups ? p.group_start[g] : 0;
+        gt->rows[g] = rows;
+        acc_tiles += (rows + BM_CTA * kCtaGroup - 1) / (BM_CTA * kCtaGroup);
+      }
+      gt->prefix[MAX_GROUPS] = acc_tiles;
+    }
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
@@ -150,8 +189,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int unit = blockIdx.x / kCtaGroup;
   const int num_units = (p.fused == 1 ? p.gemm_ctas : (int)gridDim.x) / kCtaGroup;
   const bool copy_cta = (p.fused == 1) && ((int)blockIdx.x >= p.gemm_ctas);
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
-  const int nkb = p.num_k_blocks;
+  // grouped mode 1 only knows its M tiles now; mode 2 runs the full [M, N] tile grid once per group
+  const int num_m_tiles = (p.grouped == 1) ? gt->prefix[MAX_GROUPS] : p.num_m_tiles;
+  const int tiles_per_group = num_m_tiles * p.num_n_tiles;
+  const int num_tiles = (p.grouped == 2) ? tiles_per_group * p.n_groups : tiles_per_group;
+  constexpr int TILE_M_ALL = BM_CTA * kCtaGroup;
+  // Where a tile lives.  Every role calls this with the same arguments, so all agree on the rows, the group and
+  // the contraction range (kb0 <= kb < kb1; an empty range means the tile is skipped by everybody).
+  auto locate = [&](int tile, int& tn, int& row0, int& m_limit, int& grp, int& kb0, int& kb1) {
+    int tm;
+    grp = 0;
+    kb0 = 0;
+    kb1 = p.num_k_blocks;
+    if (p.grouped == 2) {
+      grp = tile / tiles_per_group;
+      tile -= grp * tiles_per_group;
+      kb0 = gt->start[grp] / BK;
+      kb1 = (gt->start[grp] + gt->rows[grp] + BK - 1) / BK;
+      if (gt->rows[grp] == 0) kb1 = kb0;
+    }
+    tile_coords(tile, p, num_m_tiles, tm, tn);
+    row0 = tm * TILE_M_ALL;
+    m_limit = p.M;
+    if (p.grouped == 1) {
+      while (grp + 1 < MAX_GROUPS && tm >= gt->prefix[grp + 1]) ++grp;
+      row0 = gt->start[grp] + (tm - gt->prefix[grp]) * TILE_M_ALL;
+      m_limit = min(p.M, gt->start[grp] + gt->rows[grp]);
+    }
+  };
 
   if (copy_cta) {
     // ------------------------------------------------------------ all-gather copy role (mode 1)
@@ -235,10 +300,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       const uint32_t full0_remote = (kCtaGroup == 2) ? mapa_u32(smem_u32(&full[0]), 0) : 0;
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
-        int tm, tn;
-        tile_coords(tile, p, tm, tn);
-        int m0 = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA;
+        int tn, row0, m_limit, grp, kb0, kb1;
+        locate(tile, tn, row0, m_limit, grp, kb0, kb1);
+        const int tm = row0 / TILE_M_ALL;  // fused modes only (never grouped)
+        int m0 = row0 + cta_rank * BM_CTA;
         const int n0 = tn * BN + cta_rank * BN_CTA;
+        // a grouped-M GEMM reads group `grp`'s own B: a row offset for a K-major B, a k offset for an MN-major one
+        const int bn_off = (p.grouped == 1 && !p.b_mn) ? grp * p.b_group_stride : 0;
+        const int bk_off = (p.grouped == 1 && p.b_mn) ? grp * p.b_group_stride : 0;
         const CUtensorMap* tma_a = &tmA;
         if (p.fused == 1) {
           const int chunk = (tm * (BM_CTA * kCtaGroup)) / p.chunk_rows;
@@ -253,7 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             asm volatile("fence.proxy.async.global;" ::: "memory");  // copied rows -> visible to the TMA engine
           }
         }
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
@@ -270,10 +339,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d(a_dst + i * 8192, tma_a, &full[stage], m0 + i * 64, k0);
             }
             if (!p.b_mn) {
-              tma_load_2d(b_dst, &tmB, &full[stage], k0, n0);
+              tma_load_2d(b_dst, &tmB, &full[stage], k0, n0 + bn_off);
             } else {
 #pragma unroll
-              for (int i = 0; i < BN_CTA / 64; ++i) tma_load_2d(b_dst + i * 8192, &tmB, &full[stage], n0 + i * 64, k0);
+              for (int i = 0; i < BN_CTA / 64; ++i)
+                tma_load_2d(b_dst + i * 8192, &tmB, &full[stage], n0 + i * 64, k0 + bk_off);
             }
           } else {
             if (leader) mbar_expect_tx(&full[stage], STAGE_BYTES * 2);
@@ -285,10 +355,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int i = 0; i < BM_CTA / 64; ++i) tma_load_2d_pair(a_dst + i * 8192, tma_a, bar, m0 + i * 64, k0);
             }
             if (!p.b_mn) {
-              tma_load_2d_pair(b_dst, &tmB, bar, k0, n0);
+              tma_load_2d_pair(b_dst, &tmB, bar, k0, n0 + bn_off);
             } else {
 #pragma unroll
-              for (int i = 0; i < BN_CTA / 64; ++i) tma_load_2d_pair(b_dst + i * 8192, &tmB, bar, n0 + i * 64, k0);
+              for (int i = 0; i < BN_CTA / 64; ++i)
+                tma_load_2d_pair(b_dst + i * 8192, &tmB, bar, n0 + i * 64, k0 + bk_off);
             }
           }
           if (++stage == kStages) {
@@ -311,13 +382,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        int tn_, row0_, ml_, grp_, kb0, kb1;
+        locate(tile, tn_, row0_, ml_, grp_, kb0, kb1);
+        if (kb1 <= kb0) continue;  // empty group: no accumulator is produced, the epilogue skips the tile too
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             ok = false;
             break;
@@ -329,7 +403,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = make_smem_desc(a_addr + k * a_kstep, a_lbo, 1024);
             const uint64_t db = make_smem_desc(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_ss<kCtaGroup>(d_tmem, da, db, idesc, (kb | k) != 0);
+            umma_ss<kCtaGroup>(d_tmem, da, db, idesc, (kb != kb0) || (k != 0));
           }
           if constexpr (kCtaGroup == 1) umma_commit(&empty[stage]);
           else umma_commit_pair(&empty[stage], 3);
@@ -359,12 +433,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                            reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.aux)) &
                           15) == 0);
     for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
-      int tm, tn;
-      tile_coords(tile, p, tm, tn);
-      int row = tm * (BM_CTA * kCtaGroup) + cta_rank * BM_CTA + quarter * 32 + lane;
+      int tn, row0, m_limit, grp, kb0, kb1;
+      locate(tile, tn, row0, m_limit, grp, kb0, kb1);
+      if (kb1 <= kb0) continue;
+      const int tm = row0 / TILE_M_ALL;  // fused modes only
+      int row = row0 + cta_rank * BM_CTA + quarter * 32 + lane;
       const int n0 = tn * BN;
       void* c_base = p.C;
-      int m_limit = p.M;
+      if (p.grouped == 2)
+        c_base = p.out_fp32 ? static_cast<void*>(reinterpret_cast<float*>(p.C) + grp * p.c_group_stride)
+                            : static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(p.C) + grp * p.c_group_stride);
+      // grouped M: rows of this tile past the group's end are written as zeros (bf16 outputs)
+      const bool zero_tail = (p.grouped == 1) && !p.out_fp32 && row >= m_limit && row < p.M;
       bool peer_tile = false;
       if (p.fused == 2) {
         const int chunk = (tm * (BM_CTA * kCtaGroup)) / p.chunk_rows;
@@ -404,6 +484,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
+        if (zero_tail) {
+          __nv_bfloat16* zp = reinterpret_cast<__nv_bfloat16*>(c_base) + (long long)row * p.ldc + col0;
+          if (col0 + 32 <= p.N && vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(zp)[q] = make_uint4(0u, 0u, 0u, 0u);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) zp[j] = __float2bfloat16(0.f);
+          }
+        }
         if (row < m_limit) {
           float v[32];
 #pragma unroll
@@ -626,7 +715,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <int kCtaGroup, int BN, int kStages>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sm_count,
-                       cudaStream_t stream, const CUtensorMap* tmA2 = nullptr, int copy_ctas = 0) {
+                       cudaStream_t stream, const CUtensorMap* tmA2 = nullptr, int copy_ctas = 0,
+                       int tile_multiplier = 1) {
   constexpr int A_BYTES = BM_CTA * BK * 2;
   constexpr int B_BYTES = (BN / kCtaGroup) * BK * 2;
   constexpr int SMEM = kStages * (A_BYTES + B_BYTES) + 1024 + 256 + 4 * 32 * 144;
@@ -642,7 +732,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.num_n_tiles = (p.N + BN - 1) / BN;
   p.num_k_blocks = (p.K + BK - 1) / BK;
   p.group_m = kCtaGroup == 1 ? 16 : 8;
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  // grouped M: up to one partial tile per group on top of the dense count (p.M is the buffers' row capacity)
+  const int tiles = (p.num_m_tiles + (p.grouped == 1 ? p.n_groups : 0)) * p.num_n_tiles * tile_multiplier;
   int units = (sm_count - copy_ctas) / kCtaGroup;
   if (units > tiles) units = tiles;
   if (units < 1) units = 1;
@@ -737,6 +828,72 @@ int pb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
     case 3: return launch_gemm<1, 128, 6>(tmA, tmB, p, sms, stream);
     default: return -5;
   }
+}
+
+
+// Grouped GEMMs of a mixture-of-experts layer: ONE launch covers all local experts, and the group sizes stay on the
+// device (group_rows / group_start: int[n_groups] in device memory, group_start[g] a multiple of 256).
+//   mode 1 (rows grouped):  C[r, :] = A[r, :] . B_g^T for the rows r of group g.  A: [M, K] K-major, M = the row
+//       capacity of the buffers.  B: b_mn ? the groups' [K, N] matrices stacked to [n_groups * K, N]
+//                                         : the groups' [N, K] matrices stacked to [n_groups * N, K].
+//       C: [M, N] bf16.  Rows of a computed tile beyond its group's end are set to zero; tiles without rows of any
+//       group are not computed and their part of C is left untouched.  b_mn needs K % 64 == 0.
+//   mode 2 (contraction grouped):  C_g[M, N] (+)= sum over the rows r of group g of A[r, m] * B[r, n].
+//       A: [rows, M], B: [rows, N] (both MN-major), C: n_groups stacked [M, N] blocks (fp32 accumulate or bf16).
+//       Rows from a group's end to the next multiple of 64 take part: they must be zero in A or in B and finite in
+//       the other (mode 1 outputs satisfy this).
+int pb_gemm_grouped(int mode, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int b_mn, int n_groups, const int* group_rows,
+                    const int* group_start, int out_fp32, int accumulate, int* err_dev, void* stream_) {
+  using namespace pb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (mode != 1 && mode != 2) return -1;
+  if (M <= 0 || N <= 0 || K <= 0 || n_groups < 1 || n_groups > MAX_GROUPS) return -1;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (accumulate && !out_fp32) return -4;
+  if (mode == 1 && (out_fp32 || (b_mn && K % 64 != 0))) return -6;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tmA, tmB;
+  int r;
+  if (mode == 1) {
+    r = make_tmap_bf16_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128);
+    if (r) return -10;
+    if (!b_mn) r = make_tmap_bf16_2d(&tmB, B, (uint64_t)K, (uint64_t)n_groups * N, (uint64_t)ldb, 64, 128);
+    else r = make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)n_groups * K, (uint64_t)ldb, 64, 64);
+    if (r) return -11;
+  } else {
+    r = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64);
+    if (r) return -10;
+    r = make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64);
+    if (r) return -11;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.C = C;
+  p.ldc = ldc;
+  p.out_fp32 = out_fp32;
+  p.accumulate = accumulate;
+  p.a_mn = mode == 2;
+  p.b_mn = mode == 2 ? 1 : b_mn;
+  p.err = err_dev;
+  p.grouped = mode;
+  p.n_groups = n_groups;
+  p.group_rows = group_rows;
+  p.group_start = group_start;
+  p.b_group_stride = b_mn ? K : N;
+  p.c_group_stride = (long long)M * ldc;
+  int sms = sm_count - g_sm_reserve;
+  if (sms < 2) sms = 2;
+  return launch_gemm<2, 256, 6>(tmA, tmB, p, sms, stream, nullptr, 0, mode == 2 ? n_groups : 1);
 }
 
 

@@ -1,8 +1,14 @@
 // Expert-parallel MoE data movement over NVLink peer memory.
 //
-//   moe_slots     : position of every (token, k) assignment inside its expert's group (atomic histogram)
-//   moe_dispatch  : permute + all-to-all in one kernel: each assignment's token row (optionally scaled) is stored
-//                   straight into the owning rank's expert-grouped receive buffer (P2P stores)
+//   moe_route     : softmax over the router logits, top-k, normalised weights, load-balance statistics and the
+//                   position of every (token, k) assignment inside its expert's group, in token order (no atomics:
+//                   the order, and with it the summation order of the expert weight gradients, is reproducible)
+//   moe_route_bwd : gradient of the router logits from the gradients of the top-k weights and of the aux loss
+//   moe_dispatch  : count exchange + permute + all-to-all in one kernel: the ranks tell each other how many rows
+//                   they hold per expert, every rank derives the layout of every receive buffer from that (expert
+//                   groups start on multiples of 256 rows), and each assignment's token row (optionally scaled) is
+//                   stored straight into the owning rank's expert-grouped receive buffer (P2P stores).  Sizes never
+//                   visit the host: the receiver gets its group table in device memory for the grouped GEMM.
 //   moe_combine   : all-to-all + un-permute + weighted top-k sum in one kernel: each token pulls its k expert rows
 //                   from the ranks that computed them (P2P loads), fp32 accumulate; can keep the pulled rows
 //   moe_rowdot    : dots[t, k] = <dy[t], rows[t, k]>  (gradient of the router weights)
@@ -28,13 +34,198 @@ struct Comm {
   int* flags[MAX_RANKS];  // every rank's flag block: [0,W) phase A, [W,2W) phase B
   int* counter;           // local grid-barrier counter (zeroed before launch)
   int* err;
+  long long wait_cycles;
   int rank, world, epoch;
 };
 
-__global__ void moe_slots_kernel(const int* __restrict__ expert, int* __restrict__ counts, int* __restrict__ slot,
-                                 int n) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) slot[i] = atomicAdd(&counts[expert[i]], 1);
+constexpr int MAX_EXPERTS = 16;
+constexpr int ROUTE_THREADS = 256;
+
+// One thread per token.  logits: [T, ld] bf16.  Outputs: probs [T, E] fp32, topi / topw [T, k] (weights normalised
+// over the selected k), pos [T*k] = rank of the assignment among this CTA's assignments to the same expert (token
+// order), cta_counts / cta_psum [gridDim.x, E] = this CTA's assignments per expert and sums of probabilities.
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
+                                                                  int T, int E, int k, float* __restrict__ probs,
+                                                                  int* __restrict__ topi, float* __restrict__ topw,
+                                                                  int* __restrict__ pos, int* __restrict__ cta_counts,
+                                                                  float* __restrict__ cta_psum) {
+  __shared__ int s_wcnt[ROUTE_THREADS / 32][MAX_EXPERTS];
+  __shared__ float s_wsum[ROUTE_THREADS / 32][MAX_EXPERTS];
+  const int t = blockIdx.x * ROUTE_THREADS + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool live = t < T;
+  float p[MAX_EXPERTS];
+  int sel[MAX_TOPK];
+  unsigned chosen = 0;
+  if (live) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS; ++e) {
+      p[e] = e < E ? __bfloat162float(logits[(long long)t * ld + e]) : -INFINITY;
+      mx = fmaxf(mx, p[e]);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS; ++e) {
+      p[e] = e < E ? __expf(p[e] - mx) : 0.f;
+      sum += p[e];
+    }
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS; ++e) {
+      p[e] *= inv;
+      if (e < E) probs[(long long)t * E + e] = p[e];
+    }
+    float wsum = 0.f;
+    float w[MAX_TOPK];
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j) {
+      if (j >= k) continue;
+      int best = 0;
+      float bv = -1.f;
+#pragma unroll
+      for (int e = 0; e < MAX_EXPERTS; ++e)
+        if (e < E && !((chosen >> e) & 1u) && p[e] > bv) {  // ties go to the lower index, as torch.topk does
+          bv = p[e];
+          best = e;
+        }
+      chosen |= 1u << best;
+      sel[j] = best;
+      w[j] = bv;
+      wsum += bv;
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j)
+      if (j < k) {
+        topi[(long long)t * k + j] = sel[j];
+        topw[(long long)t * k + j] = w[j] / wsum;
+      }
+  } else {
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS; ++e) p[e] = 0.f;
+  }
+  // per expert: how many tokens of this warp chose it, and which of them come before this token
+  int rank_in_warp[MAX_EXPERTS];
+#pragma unroll
+  for (int e = 0; e < MAX_EXPERTS; ++e) {
+    if (e >= E) continue;
+    const unsigned m = __ballot_sync(0xffffffffu, (chosen >> e) & 1u);
+    rank_in_warp[e] = __popc(m & ((1u << lane) - 1u));
+    float v = p[e];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) {
+      s_wcnt[warp][e] = __popc(m);
+      s_wsum[warp][e] = v;
+    }
+  }
+  __syncthreads();
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j) {
+      if (j >= k) continue;
+      int base = 0;
+      int r = 0;
+#pragma unroll
+      for (int e = 0; e < MAX_EXPERTS; ++e)
+        if (e == sel[j]) r = rank_in_warp[e];
+      for (int w2 = 0; w2 < warp; ++w2) base += s_wcnt[w2][sel[j]];
+      pos[(long long)t * k + j] = base + r;
+    }
+  }
+  if (threadIdx.x < E) {
+    int c = 0;
+    float ps = 0.f;
+    for (int w2 = 0; w2 < ROUTE_THREADS / 32; ++w2) {
+      c += s_wcnt[w2][threadIdx.x];
+      ps += s_wsum[w2][threadIdx.x];
+    }
+    cta_counts[blockIdx.x * E + threadIdx.x] = c;
+    cta_psum[blockIdx.x * E + threadIdx.x] = ps;
+  }
+}
+
+// One CTA: prefix over the route kernel's CTAs (in order), totals, the load-balance loss, final positions.
+//   counts[e] = assignments to e; share[e] = counts[e] / (T k); aux = E * sum_e share[e] * mean_t probs[t, e]
+__global__ void __launch_bounds__(1024) moe_route_finish_kernel(int* __restrict__ cta_counts,
+                                                                const float* __restrict__ cta_psum, int n_cta, int T,
+                                                                int E, int k, const int* __restrict__ topi,
+                                                                int* __restrict__ pos, int* __restrict__ counts,
+                                                                float* __restrict__ share, float* __restrict__ aux) {
+  __shared__ float s_term[MAX_EXPERTS];
+  if (threadIdx.x < E) {
+    const int e = threadIdx.x;
+    int run = 0;
+    float ps = 0.f;
+    for (int c = 0; c < n_cta; ++c) {
+      const int v = cta_counts[c * E + e];
+      cta_counts[c * E + e] = run;  // becomes the CTA's base
+      run += v;
+      ps += cta_psum[c * E + e];
+    }
+    counts[e] = run;
+    const float sh = (float)run / (float)((long long)T * k);
+    share[e] = sh;
+    s_term[e] = sh * (ps / (float)T);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int e = 0; e < E; ++e) a += s_term[e];
+    *aux = a * (float)E;
+  }
+  const long long n = (long long)T * k;
+  for (long long a = threadIdx.x; a < n; a += blockDim.x)
+    pos[a] += cta_counts[(int)((a / k) / ROUTE_THREADS) * E + topi[a]];
+}
+
+// dlogits[t, :] from g_w [T, k] (gradient of the normalised top-k weights) and *g_aux (gradient of the aux loss).
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_bwd_kernel(const float* __restrict__ probs,
+                                                                      const int* __restrict__ topi,
+                                                                      const float* __restrict__ topw,
+                                                                      const float* __restrict__ g_w,
+                                                                      const float* __restrict__ g_aux,
+                                                                      const float* __restrict__ share, int T, int E,
+                                                                      int k, __nv_bfloat16* __restrict__ dlogits,
+                                                                      int ld) {
+  const int t = blockIdx.x * ROUTE_THREADS + threadIdx.x;
+  if (t >= T) return;
+  float p[MAX_EXPERTS], dp[MAX_EXPERTS];
+  const float ga = g_aux ? *g_aux : 0.f;
+#pragma unroll
+  for (int e = 0; e < MAX_EXPERTS; ++e) {
+    p[e] = e < E ? probs[(long long)t * E + e] : 0.f;
+    dp[e] = e < E ? ga * (float)E * share[e] / (float)T : 0.f;
+  }
+  if (g_w) {
+    float s = 0.f, gdotw = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j)
+      if (j < k) {
+        const int e = topi[(long long)t * k + j];
+#pragma unroll
+        for (int q = 0; q < MAX_EXPERTS; ++q)
+          if (q == e) s += p[q];
+        gdotw += g_w[(long long)t * k + j] * topw[(long long)t * k + j];
+      }
+    const float inv_s = 1.f / s;
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j)
+      if (j < k) {
+        const int e = topi[(long long)t * k + j];
+        const float g = (g_w[(long long)t * k + j] - gdotw) * inv_s;
+#pragma unroll
+        for (int q = 0; q < MAX_EXPERTS; ++q)
+          if (q == e) dp[q] += g;
+      }
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < MAX_EXPERTS; ++e) dot += dp[e] * p[e];
+#pragma unroll
+  for (int e = 0; e < MAX_EXPERTS; ++e)
+    if (e < ld) dlogits[(long long)t * ld + e] = __float2bfloat16(e < E ? p[e] * (dp[e] - dot) : 0.f);
+  for (int e = MAX_EXPERTS; e < ld; ++e) dlogits[(long long)t * ld + e] = __float2bfloat16(0.f);  // padding columns
 }
 
 __device__ __forceinline__ bool handshake(const Comm& c, int phase) {
@@ -43,23 +234,74 @@ __device__ __forceinline__ bool handshake(const Comm& c, int phase) {
     st_release_sys(c.flags[threadIdx.x] + phase * c.world + c.rank, c.epoch);
   bool ok = true;
   if ((int)threadIdx.x < c.world && (int)threadIdx.x != c.rank)
-    ok = wait_flag_sys(c.flags[c.rank] + phase * c.world + threadIdx.x, c.epoch, c.err, 3);
+    ok = wait_flag_sys(c.flags[c.rank] + phase * c.world + threadIdx.x, c.epoch, c.err, 3, c.wait_cycles);
   return __syncthreads_and(ok);
 }
 
-// x: [T, H] bf16; expert/slot: [T*k]; dst_base[e]: first row of this rank's block inside expert e's group on its
-// owner; recv[r]: every rank's receive buffer [rows, H]; scale: optional [T*k] fp32.
+constexpr int ERR_CAPACITY = 4;
+
+// x: [T, H] bf16; expert/slot: [T*k]; counts: this rank's assignments per expert [E]; cnt[r]: every rank's [W, E]
+// count table (row s = what rank s holds); recv[r]: every rank's receive buffer [cap_rows, H]; scale: optional [T*k]
+// fp32.  Outputs on this rank: dst_base[e] = first row of this rank's block inside expert e's group on its owner
+// (what the combine needs), group_rows / group_start [experts_per_rank] = the layout of this rank's own receive
+// buffer (what the grouped GEMM needs).
 __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
                                                                const int* __restrict__ expert,
                                                                const int* __restrict__ slot,
-                                                               const int* __restrict__ dst_base,
+                                                               const int* __restrict__ counts,
                                                                const float* __restrict__ scale,
-                                                               __nv_bfloat16* const* __restrict__ recv_ptrs, int T,
-                                                               int k, int H, int experts_per_rank, Comm c) {
+                                                               __nv_bfloat16* const* __restrict__ recv_ptrs,
+                                                               int* const* __restrict__ cnt_ptrs, int T, int k, int H,
+                                                               int E, int experts_per_rank, int cap_rows,
+                                                               int* __restrict__ dst_base_out,
+                                                               int* __restrict__ group_rows_out,
+                                                               int* __restrict__ group_start_out, Comm c) {
   __shared__ __nv_bfloat16* s_recv[MAX_RANKS];
-  if (threadIdx.x < MAX_RANKS) s_recv[threadIdx.x] = threadIdx.x < c.world ? recv_ptrs[threadIdx.x] : nullptr;
+  __shared__ int s_cnt[MAX_RANKS][MAX_EXPERTS];
+  __shared__ int s_total[MAX_EXPERTS], s_base[MAX_EXPERTS];
+  const int W = c.world;
+  if (threadIdx.x < MAX_RANKS) s_recv[threadIdx.x] = (int)threadIdx.x < W ? recv_ptrs[threadIdx.x] : nullptr;
+  // phase 0: "my receive buffer is free, and this is how many rows I hold for each expert"
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < W * E; i += THREADS) {
+      const int q = i / E, e = i % E;
+      cnt_ptrs[q][c.rank * E + e] = counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < W) st_release_sys(c.flags[threadIdx.x] + c.rank, c.epoch);
+  }
+  bool ok = true;
+  if ((int)threadIdx.x < W) ok = wait_flag_sys(c.flags[c.rank] + threadIdx.x, c.epoch, c.err, 3, c.wait_cycles);
+  if (!__syncthreads_and(ok)) return;
+  {
+    const int* mine = cnt_ptrs[c.rank];
+    for (int i = threadIdx.x; i < W * E; i += THREADS) s_cnt[i / E][i % E] = mine[i];
+  }
   __syncthreads();
-  if (!handshake(c, 0)) return;  // every peer's receive buffer is free
+  if ((int)threadIdx.x < E) {
+    int tot = 0;
+    for (int s_ = 0; s_ < W; ++s_) tot += s_cnt[s_][threadIdx.x];
+    s_total[threadIdx.x] = tot;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < E) {
+    const int e = threadIdx.x, d = e / experts_per_rank;
+    int start = 0;
+    for (int h = d * experts_per_rank; h < e; ++h) start += (s_total[h] + 255) / 256 * 256;
+    int before = 0;
+    for (int s_ = 0; s_ < c.rank; ++s_) before += s_cnt[s_][e];
+    s_base[e] = start + before;
+    if (start + s_total[e] > cap_rows) atomicExch(c.err, ERR_CAPACITY);  // rows past the capacity are dropped below
+    if (blockIdx.x == 0) {
+      dst_base_out[e] = start + before;
+      if (d == c.rank) {
+        group_rows_out[e - d * experts_per_rank] = min(s_total[e], max(cap_rows - start, 0));
+        group_start_out[e - d * experts_per_rank] = min(start, cap_rows / 256 * 256);
+      }
+    }
+  }
+  __syncthreads();
   const int warps_per_block = THREADS / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vec = H / 8;
@@ -67,7 +309,8 @@ __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat
   for (long long a = blockIdx.x * warps_per_block + warp; a < n; a += (long long)gridDim.x * warps_per_block) {
     const int e = expert[a];
     const int d = e / experts_per_rank;
-    const long long row = (long long)dst_base[e] + slot[a];
+    const long long row = (long long)s_base[e] + slot[a];
+    if (row >= cap_rows) continue;
     const uint4* src = reinterpret_cast<const uint4*>(x + (a / k) * H);
     uint4* dst = reinterpret_cast<uint4*>(s_recv[d] + row * H);
     const float s = scale ? scale[a] : 1.f;
@@ -93,7 +336,7 @@ __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat
     }
   }
   __threadfence_system();
-  if (!grid_barrier(c.counter, (int)gridDim.x, c.err, 3)) return;
+  if (!grid_barrier(c.counter, (int)gridDim.x, c.err, 3, c.wait_cycles)) return;
   handshake(c, 1);  // everything destined to me has landed when every peer reports "pushed"
 }
 
@@ -158,7 +401,7 @@ __global__ void __launch_bounds__(THREADS) moe_combine_kernel(__nv_bfloat16* __r
       }
     }
   }
-  if (!grid_barrier(c.counter, (int)gridDim.x, c.err, 3)) return;
+  if (!grid_barrier(c.counter, (int)gridDim.x, c.err, 3, c.wait_cycles)) return;
   handshake(c, 1);  // peers may reuse their output buffers once everybody has finished reading
 }
 
@@ -190,6 +433,7 @@ static Comm make_comm(int** flags, int* counter, int* err, int rank, int world, 
   for (int i = 0; i < MAX_RANKS; ++i) c.flags[i] = i < world ? flags[i] : nullptr;
   c.counter = counter;
   c.err = err;
+  c.wait_cycles = pb_peer_wait_cycles();
   c.rank = rank;
   c.world = world;
   c.epoch = epoch;
@@ -200,28 +444,51 @@ static Comm make_comm(int** flags, int* counter, int* err, int rank, int world, 
 
 extern "C" {
 
-int pb_moe_slots(const int* expert, int* counts, int* slot, int n, int n_experts, void* stream_) {
+// Router: logits [T, ld] bf16 -> probs [T, E], topi / topw [T, k], slot [T*k] (position inside the expert's group of
+// this rank's assignments, token order), counts [E], share [E], aux (scalar).  scratch_i: int[n_cta * E],
+// scratch_f: float[n_cta * E] with n_cta = ceil(T / 256).  E <= 16, k <= 4.
+int pb_moe_route(const void* logits, int ld, int T, int E, int k, float* probs, int* topi, float* topw, int* slot,
+                 int* counts, float* share, float* aux, int* scratch_i, float* scratch_f, void* stream_) {
+  using namespace pbmoe;
+  if (E < 1 || E > MAX_EXPERTS || k < 1 || k > MAX_TOPK || k > E || ld < E || T < 1) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  cudaError_t e = cudaMemsetAsync(counts, 0, n_experts * sizeof(int), stream);
-  if (e != cudaSuccess) return (int)e;
-  pbmoe::moe_slots_kernel<<<(n + 255) / 256, 256, 0, stream>>>(expert, counts, slot, n);
+  const int n_cta = (T + ROUTE_THREADS - 1) / ROUTE_THREADS;
+  moe_route_kernel<<<n_cta, ROUTE_THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, T, E, k,
+                                                        probs, topi, topw, slot, scratch_i, scratch_f);
+  moe_route_finish_kernel<<<1, 1024, 0, stream>>>(scratch_i, scratch_f, n_cta, T, E, k, topi, slot, counts, share,
+                                                  aux);
+  pb_count_launch(2);
+  return (int)cudaGetLastError();
+}
+
+// g_w: [T, k] fp32 or null; g_aux: device scalar or null.
+int pb_moe_route_bwd(const float* probs, const int* topi, const float* topw, const float* g_w, const float* g_aux,
+                     const float* share, int T, int E, int k, void* dlogits, int ld, void* stream_) {
+  using namespace pbmoe;
+  if (E < 1 || E > MAX_EXPERTS || k < 1 || k > MAX_TOPK || ld < E) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  moe_route_bwd_kernel<<<(T + ROUTE_THREADS - 1) / ROUTE_THREADS, ROUTE_THREADS, 0, stream>>>(
+      probs, topi, topw, g_w, g_aux, share, T, E, k, reinterpret_cast<__nv_bfloat16*>(dlogits), ld);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
 
-// recv_ptrs_dev / y_ptrs_dev: device arrays of `world` pointers. counter: local int, zeroed here.
-int pb_moe_dispatch(const void* x, const int* expert, const int* slot, const int* dst_base, const float* scale,
-                    void* recv_ptrs_dev, int T, int k, int H, int experts_per_rank, int** flags, int* counter,
-                    int* err, int rank, int world, int epoch, int ctas, void* stream_) {
+// recv_ptrs_dev / cnt_ptrs_dev / y_ptrs_dev: device arrays of `world` pointers. counter: local int, zeroed here.
+// A receive buffer that would overflow `cap_rows` sets the device error word to 4 and drops the rows beyond it.
+int pb_moe_dispatch(const void* x, const int* expert, const int* slot, const int* counts, const float* scale,
+                    void* recv_ptrs_dev, void* cnt_ptrs_dev, int T, int k, int H, int E, int experts_per_rank,
+                    int cap_rows, int* dst_base_out, int* group_rows_out, int* group_start_out, int** flags,
+                    int* counter, int* err, int rank, int world, int epoch, int ctas, void* stream_) {
   using namespace pbmoe;
-  if (H % 8 != 0 || world > MAX_RANKS) return -1;
+  if (H % 8 != 0 || world > MAX_RANKS || E > MAX_EXPERTS || E % world != 0 || experts_per_rank * world != E) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
-  moe_dispatch_kernel<<<ctas, THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), expert, slot, dst_base,
-                                                    scale, reinterpret_cast<__nv_bfloat16* const*>(recv_ptrs_dev), T,
-                                                    k, H, experts_per_rank,
-                                                    make_comm(flags, counter, err, rank, world, epoch));
+  moe_dispatch_kernel<<<ctas, THREADS, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), expert, slot, counts, scale,
+      reinterpret_cast<__nv_bfloat16* const*>(recv_ptrs_dev), reinterpret_cast<int* const*>(cnt_ptrs_dev), T, k, H, E,
+      experts_per_rank, cap_rows, dst_base_out, group_rows_out, group_start_out,
+      make_comm(flags, counter, err, rank, world, epoch));
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

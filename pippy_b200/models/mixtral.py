@@ -76,7 +76,7 @@ class MixtralStage(nn.Module):
         return h.view(B, S, -1)
 
     def expert_parameters(self):
-        return [p for n, p in self.named_parameters() if ".w_gate_up." in n or ".w_down." in n]
+        return [p for n, p in self.named_parameters() if n.endswith(".w_gate_up") or n.endswith(".w_down")]
 
     def dense_parameters(self):
         experts = {id(p) for p in self.expert_parameters()}

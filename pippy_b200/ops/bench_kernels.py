@@ -258,27 +258,27 @@ def bench_moe():
     Launch with: python -m torch.distributed.run --nproc-per-node W -m pippy_b200.ops.bench_kernels moe"""
     import torch.distributed as dist
 
-    from ..parallel.ep import EPContext, _Plan
+    from ..parallel.ep import EPContext, _Plan, _RouteFn
 
     rank, W = _dist_setup()
     T, H, E, K = 8192, 4096, 8, 2
-    ep = EPContext(None, max_tokens=T, hidden=H, top_k=K)
+    ep = EPContext(None, max_tokens=T, hidden=H, top_k=K, n_experts=E)
     g = torch.Generator(device="cuda").manual_seed(rank)
     x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
-    logits = torch.randn(T, E, device="cuda", generator=g)
-    wgt, idx = torch.softmax(logits, -1).topk(K, dim=-1)
-    expert = idx.to(torch.int32).reshape(-1).contiguous()
-    weight = (wgt / wgt.sum(-1, keepdim=True)).float().reshape(-1).contiguous()
-    plan = _Plan(ep, expert, E)
+    logits = torch.randn(T, E, device="cuda", generator=g).bfloat16()
+    plan = _Plan(ep, T)
+    topw, _ = _RouteFn.apply(logits, plan, E, K)
+    expert = plan.expert
+    weight = topw.reshape(-1).contiguous()
     out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
     save = torch.empty(T * K, H, device="cuda", dtype=torch.bfloat16)
     epr = E // W
 
     def fused_dispatch():
-        ep.dispatch(x, expert, plan.slot, plan.dst_base, None, epr)
+        ep.dispatch(x, plan, None)
 
     def fused_combine():
-        ep.combine(out, expert, plan.slot, plan.dst_base, weight, save, epr)
+        ep.combine(out, plan, weight, save)
 
     # the library way: sort assignments by destination expert, exchange counts-sized slabs, un-sort and weight
     order = torch.argsort(expert.long(), stable=True)

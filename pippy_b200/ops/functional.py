@@ -111,21 +111,28 @@ class _LinearFn(torch.autograd.Function):
         weight._pb_direct_grad = True
         if bias is not None:
             bias._pb_direct_grad = True
-        ctx.save_for_backward(x2, weight, aux)
+        # Parameters ride on ctx, not in save_for_backward: saved tensors pass through the saved-tensor hooks of
+        # activation checkpointing, which hand the backward a detached stand-in without `main_grad` or
+        # `requires_grad`, and the weight gradient would be written to an object nobody reads.
+        ctx.save_for_backward(x2, aux)
+        ctx.weight = weight
         ctx.bias = bias
         ctx.act = act
         ctx.has_residual = residual is not None
+        ctx.res_shape = residual.shape if residual is not None else None
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], weight.shape[0])
+        # 2-D in, 2-D out: the result is returned as allocated, never as a view made in here (autograd refuses
+        # in-place changes, such as the rotary embedding of a qkv projection, to views created inside a Function)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, aux = ctx.saved_tensors
-        bias = ctx.bias
+        x2, aux = ctx.saved_tensors
+        weight, bias = ctx.weight, ctx.bias
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dres = dy if ctx.has_residual else None
+        dres = dy.reshape(ctx.res_shape) if ctx.has_residual else None
         if ctx.act == ACT_GELU_TANH:
             dpre = torch.empty_like(dy2)
             _lib.check(
@@ -148,7 +155,8 @@ def linear(x, weight, bias=None, residual=None, activation: Optional[str] = None
         act = ACT_GELU_TANH if activation == "gelu_tanh" else ACT_NONE
         if activation not in (None, "gelu_tanh"):
             raise ValueError(f"unsupported fused activation {activation!r}")
-        return _LinearFn.apply(x, weight, bias, residual, act)
+        y = _LinearFn.apply(x, weight, bias, residual, act)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
     y = F.linear(x, weight, bias)
     if activation == "gelu_tanh":
         y = F.gelu(y, approximate="tanh")
@@ -203,7 +211,8 @@ class _NormFn(torch.autograd.Function):
                                    _lib.c_int(int(layer)), _lib.stream_ptr()),
             "pb_norm_fwd",
         )
-        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.save_for_backward(x2, mean, rstd)
+        ctx.weight = weight  # not a saved tensor: see _LinearFn.forward
         weight._pb_direct_grad = True
         if bias is not None:
             bias._pb_direct_grad = True
@@ -214,8 +223,8 @@ class _NormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, mean, rstd = ctx.saved_tensors
-        bias = ctx.bias
+        x2, mean, rstd = ctx.saved_tensors
+        weight, bias = ctx.weight, ctx.bias
         T, H = x2.shape
         dy2 = dy.reshape(T, H)
         if not dy2.is_contiguous():

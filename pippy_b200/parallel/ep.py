@@ -1,23 +1,30 @@
 """Expert parallelism for sparse MoE layers (top-k routing, SwiGLU experts) on fused NVLink kernels.
 
-Per MoE layer and microbatch, on every rank of the expert-parallel group:
+Per MoE layer and microbatch, on every rank of the expert-parallel group, with no host synchronisation anywhere
+(every size that depends on the routing stays in device memory):
 
-  route      router GEMM (tcgen05) -> softmax / top-k / load-balance statistics on the tiny [T, E] tensor
-  dispatch   ONE kernel permutes the token rows and stores each straight into the receive buffer of the rank that
-             owns the expert, grouped by expert (``csrc/moe.cu``: P2P stores, flag handshakes)
-  experts    the local experts run the package's GEMM / SwiGLU kernels on their contiguous row groups
+  route      router GEMM (tcgen05), then ONE kernel pair: softmax, top-k, normalised weights, load-balance loss and
+             the position of each assignment inside its expert's group (``csrc/moe.cu``)
+  dispatch   ONE kernel: the ranks exchange their per-expert row counts through peer memory, derive the layout of
+             every receive buffer from them, permute the token rows and store each straight into the receive buffer
+             of the rank that owns the expert, grouped by expert (P2P stores, flag handshakes)
+  experts    ONE grouped tcgen05 GEMM launch per projection over all local experts; the kernel reads the group
+             table the dispatch left in device memory and runs only the tiles that hold rows (``csrc/gemm.cu``)
   combine    ONE kernel pulls every token's k expert rows back from the owning ranks, un-permutes and forms the
              weighted sum in fp32
 
 Backward swaps the roles: the gradient of ``combine`` is a dispatch of ``w * dy`` rows (plus a row-dot kernel for
-the router-weight gradients), the gradient of ``dispatch`` is a combine with unit weights.  Only the [world, E]
-assignment counts travel through NCCL (32 bytes per rank).  The reference has no expert parallelism; its MoE example
-places whole experts on pipeline stages (examples/mixture_of_experts/dist_moe.py:43-59).
+the router-weight gradients), the gradient of ``dispatch`` is a combine with unit weights, the expert weight
+gradients are one grouped GEMM per projection whose contraction runs over each expert's rows.  Receive buffers have a
+fixed capacity (``capacity_factor`` times the even share); a routing that would overflow it raises the device error
+word (checked by ``ops._lib.check_device_errors``) instead of writing out of bounds.  The reference has no expert
+parallelism; its MoE example places whole experts on pipeline stages
+(examples/mixture_of_experts/dist_moe.py:43-59).
 """
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist
@@ -26,29 +33,44 @@ import torch.nn.functional as F
 
 from ..ops import _lib
 from ..ops import functional as pf
+from ..ops.functional import _run_or_defer
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
 
 
 class EPContext:
-    """Peer-mapped workspaces of one expert-parallel group, shared by all MoE layers (calls are stream ordered)."""
+    """Peer-mapped workspaces of one expert-parallel group, shared by all MoE layers (calls are stream ordered).
 
-    def __init__(self, group: Optional[dist.ProcessGroup], max_tokens: int, hidden: int, top_k: int = 2, device=None,
-                 ctas: int = 96):
+    ``capacity`` rows fit into a rank's receive buffer: ``capacity_factor`` times the rows it gets when the routing is
+    perfectly even (``max_tokens * top_k``), plus the padding that lets every expert's group start on a multiple of
+    256 rows."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup], max_tokens: int, hidden: int, top_k: int = 2,
+                 n_experts: int = 8, device=None, ctas: int = 96, capacity_factor: float = 2.0):
         from ..comm.symm import SymmetricBuffer
 
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.hidden, self.top_k, self.ctas = hidden, top_k, ctas
-        self.capacity = self.world * max_tokens * top_k  # worst case: every assignment of every rank lands here
+        self.hidden, self.top_k, self.ctas, self.n_experts = hidden, top_k, ctas, n_experts
+        if n_experts % self.world != 0:
+            raise ValueError(f"{n_experts} experts cannot be spread evenly over {self.world} ranks")
+        self.experts_per_rank = n_experts // self.world
+        even = max_tokens * top_k
+        self.capacity = _align(int(even * min(capacity_factor, float(self.world))), 256) + 256 * self.experts_per_rank
         nbytes = self.capacity * hidden * 2
         self.recv = SymmetricBuffer(nbytes, group, self.device)
         self.ybuf = SymmetricBuffer(nbytes, group, self.device)
+        self.cnt = SymmetricBuffer(self.world * n_experts * 4, group, self.device)
         self.flags_d = SymmetricBuffer(4096, group, self.device)
         self.flags_c = SymmetricBuffer(4096, group, self.device)
         self.counter = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.recv_ptrs = torch.tensor(self.recv.ptrs, dtype=torch.int64, device=self.device)
         self.y_ptrs = torch.tensor(self.ybuf.ptrs, dtype=torch.int64, device=self.device)
+        self.cnt_ptrs = torch.tensor(self.cnt.ptrs, dtype=torch.int64, device=self.device)
         self.epoch_d = 0
         self.epoch_c = 0
 
@@ -58,85 +80,167 @@ class EPContext:
             arr[i] = ctypes.cast(ctypes.c_void_p(ptr), ctypes.POINTER(ctypes.c_int))
         return arr
 
-    def recv_rows(self, n: int) -> torch.Tensor:
-        return self.recv.tensor(torch.bfloat16, n * self.hidden).view(n, self.hidden)
+    def recv_rows(self) -> torch.Tensor:
+        return self.recv.tensor(torch.bfloat16, self.capacity * self.hidden).view(self.capacity, self.hidden)
 
-    def y_rows(self, n: int) -> torch.Tensor:
-        return self.ybuf.tensor(torch.bfloat16, n * self.hidden).view(n, self.hidden)
+    def y_rows(self) -> torch.Tensor:
+        return self.ybuf.tensor(torch.bfloat16, self.capacity * self.hidden).view(self.capacity, self.hidden)
 
-    def dispatch(self, x, expert, slot, dst_base, scale, experts_per_rank):
+    def dispatch(self, x, plan: "_Plan", scale) -> None:
         T = x.shape[0]
         self.epoch_d += 1
         rc = _lib.lib().pb_moe_dispatch(
-            _lib.ptr(x), _lib.ptr(expert), _lib.ptr(slot), _lib.ptr(dst_base), _lib.ptr(scale),
-            _lib.ptr(self.recv_ptrs), _lib.c_int(T), _lib.c_int(self.top_k), _lib.c_int(self.hidden),
-            _lib.c_int(experts_per_rank), self._flags(self.flags_d), _lib.ptr(self.counter),
+            _lib.ptr(x), _lib.ptr(plan.expert), _lib.ptr(plan.slot), _lib.ptr(plan.counts), _lib.ptr(scale),
+            _lib.ptr(self.recv_ptrs), _lib.ptr(self.cnt_ptrs), _lib.c_int(T), _lib.c_int(self.top_k),
+            _lib.c_int(self.hidden), _lib.c_int(self.n_experts), _lib.c_int(self.experts_per_rank),
+            _lib.c_int(self.capacity), _lib.ptr(plan.dst_base), _lib.ptr(plan.group_rows),
+            _lib.ptr(plan.group_start), self._flags(self.flags_d), _lib.ptr(self.counter),
             _lib.ptr(_lib.err_word(x.device)), _lib.c_int(self.rank), _lib.c_int(self.world),
             _lib.c_int(self.epoch_d), _lib.c_int(self.ctas), _lib.stream_ptr())
         _lib.check(rc, "pb_moe_dispatch")
 
-    def combine(self, out, expert, slot, dst_base, weight, save, experts_per_rank):
+    def combine(self, out, plan: "_Plan", weight, save) -> None:
         T = out.shape[0]
         self.epoch_c += 1
         rc = _lib.lib().pb_moe_combine(
-            _lib.ptr(out), _lib.ptr(expert), _lib.ptr(slot), _lib.ptr(dst_base), _lib.ptr(weight),
+            _lib.ptr(out), _lib.ptr(plan.expert), _lib.ptr(plan.slot), _lib.ptr(plan.dst_base), _lib.ptr(weight),
             _lib.ptr(self.y_ptrs), _lib.ptr(save), _lib.c_int(T), _lib.c_int(self.top_k), _lib.c_int(self.hidden),
-            _lib.c_int(experts_per_rank), self._flags(self.flags_c), _lib.ptr(self.counter[1:]),
+            _lib.c_int(self.experts_per_rank), self._flags(self.flags_c), _lib.ptr(self.counter[1:]),
             _lib.ptr(_lib.err_word(out.device)), _lib.c_int(self.rank), _lib.c_int(self.world),
             _lib.c_int(self.epoch_c), _lib.c_int(self.ctas), _lib.stream_ptr())
         _lib.check(rc, "pb_moe_combine")
 
 
 class _Plan:
-    """Routing result of one layer call, shared by the dispatch and combine autograd nodes."""
+    """Routing result of one layer call, all in device memory, shared by the autograd nodes of the layer."""
 
-    def __init__(self, ep: EPContext, expert: torch.Tensor, n_experts: int):
+    def __init__(self, ep: EPContext, T: int):
+        dev = ep.device
+        E, k = ep.n_experts, ep.top_k
         self.ep = ep
-        self.expert = expert  # int32 [T*k]
-        self.n_experts = n_experts
-        self.experts_per_rank = n_experts // ep.world
-        n = expert.numel()
-        counts = torch.empty(n_experts, dtype=torch.int32, device=expert.device)
-        self.slot = torch.empty(n, dtype=torch.int32, device=expert.device)
-        _lib.check(_lib.lib().pb_moe_slots(_lib.ptr(expert), _lib.ptr(counts), _lib.ptr(self.slot), _lib.c_int(n),
-                                           _lib.c_int(n_experts), _lib.stream_ptr()), "pb_moe_slots")
-        if ep.world > 1:
-            allc = torch.empty(ep.world, n_experts, dtype=torch.int32, device=expert.device)
-            dist.all_gather_into_tensor(allc, counts, group=ep.group)
+        self.T = T
+        self.expert = torch.empty(T * k, dtype=torch.int32, device=dev)   # expert of assignment (t, j)
+        self.slot = torch.empty(T * k, dtype=torch.int32, device=dev)     # its position among this rank's rows for that expert
+        self.counts = torch.empty(E, dtype=torch.int32, device=dev)       # this rank's rows per expert
+        self.share = torch.empty(E, dtype=torch.float32, device=dev)
+        self.dst_base = torch.empty(E, dtype=torch.int32, device=dev)     # filled by the dispatch kernel
+        self.group_rows = torch.zeros(ep.experts_per_rank, dtype=torch.int32, device=dev)
+        self.group_start = torch.zeros(ep.experts_per_rank, dtype=torch.int32, device=dev)
+
+
+class _RouteFn(torch.autograd.Function):
+    """logits [T, E_pad] -> (normalised top-k weights [T, k] fp32, load-balance loss); indices, positions and counts
+    go into ``plan``."""
+
+    @staticmethod
+    def forward(ctx, logits, plan: _Plan, E: int, k: int):
+        T, ld = logits.shape
+        dev = logits.device
+        probs = torch.empty(T, E, dtype=torch.float32, device=dev)
+        topw = torch.empty(T, k, dtype=torch.float32, device=dev)
+        aux = torch.empty((), dtype=torch.float32, device=dev)
+        n_cta = (T + 255) // 256
+        scratch_i = torch.empty(n_cta * E, dtype=torch.int32, device=dev)
+        scratch_f = torch.empty(n_cta * E, dtype=torch.float32, device=dev)
+        _lib.check(_lib.lib().pb_moe_route(
+            _lib.ptr(logits), _lib.c_int(ld), _lib.c_int(T), _lib.c_int(E), _lib.c_int(k), _lib.ptr(probs),
+            _lib.ptr(plan.expert), _lib.ptr(topw), _lib.ptr(plan.slot), _lib.ptr(plan.counts), _lib.ptr(plan.share),
+            _lib.ptr(aux), _lib.ptr(scratch_i), _lib.ptr(scratch_f), _lib.stream_ptr()), "pb_moe_route")
+        ctx.save_for_backward(probs, topw)
+        ctx.plan, ctx.dims = plan, (T, E, k, ld)
+        return topw, aux
+
+    @staticmethod
+    def backward(ctx, g_w, g_aux):
+        probs, topw = ctx.saved_tensors
+        plan = ctx.plan
+        T, E, k, ld = ctx.dims
+        dlogits = torch.empty(T, ld, dtype=torch.bfloat16, device=probs.device)
+        g_w = None if g_w is None else g_w.float().contiguous()
+        g_aux = None if g_aux is None else g_aux.float().contiguous()
+        _lib.check(_lib.lib().pb_moe_route_bwd(
+            _lib.ptr(probs), _lib.ptr(plan.expert), _lib.ptr(topw), _lib.ptr(g_w), _lib.ptr(g_aux),
+            _lib.ptr(plan.share), _lib.c_int(T), _lib.c_int(E), _lib.c_int(k), _lib.ptr(dlogits), _lib.c_int(ld),
+            _lib.stream_ptr()), "pb_moe_route_bwd")
+        return dlogits, None, None, None
+
+
+def grouped_gemm(mode: int, a, b, out, n, k_dim, plan: _Plan, b_mn: bool = False, accumulate: bool = False):
+    """Thin wrapper of ``pb_gemm_grouped``: ``mode`` 1 groups the rows of ``a`` / ``out``, 2 the contraction."""
+    G = plan.ep.experts_per_rank
+    M = a.shape[0] if mode == 1 else a.shape[1]
+    rc = _lib.lib().pb_gemm_grouped(
+        _lib.c_int(mode), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.c_int(M), _lib.c_int(n), _lib.c_int(k_dim),
+        _lib.c_ll(a.stride(0)), _lib.c_ll(b.stride(-2)), _lib.c_ll(out.stride(-2)), _lib.c_int(int(b_mn)),
+        _lib.c_int(G), _lib.ptr(plan.group_rows), _lib.ptr(plan.group_start),
+        _lib.c_int(int(out.dtype == torch.float32)), _lib.c_int(int(accumulate)),
+        _lib.ptr(_lib.err_word(a.device)), _lib.stream_ptr())
+    _lib.check(rc, "pb_gemm_grouped")
+    return out
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """``y[r] = a[r] @ weight[g].T`` for the rows r of local expert g; ``weight`` is ``[G, N, K]``.  ``out`` /
+    ``dgrad_out`` let the caller place the result (and the input gradient) in a buffer of its choice, e.g. the
+    peer-mapped buffer the combine kernel reads."""
+
+    @staticmethod
+    def forward(ctx, a, weight, plan: _Plan, out, dgrad_out):
+        G, N, K = weight.shape
+        if out is None:
+            out = torch.empty(a.shape[0], N, dtype=torch.bfloat16, device=a.device)
         else:
-            allc = counts.view(1, -1)
-        c = allc.cpu().tolist()  # [src][expert]; the one host sync of the layer: buffer sizes depend on it
-        W, E, epr = ep.world, n_experts, self.experts_per_rank
-        totals = [sum(c[s][e] for s in range(W)) for e in range(E)]
-        dst_base = [0] * E
-        for d in range(W):
-            start = 0
-            for e in range(d * epr, (d + 1) * epr):
-                dst_base[e] = start + sum(c[s][e] for s in range(ep.rank))
-                start += totals[e]
-        self.dst_base = torch.tensor(dst_base, dtype=torch.int32, device=expert.device)
-        mine = range(ep.rank * epr, (ep.rank + 1) * epr)
-        self.local_totals: List[int] = [totals[e] for e in mine]
-        self.recv_total = sum(self.local_totals)
-        if self.recv_total > ep.capacity:
-            raise RuntimeError(f"MoE receive buffer too small: {self.recv_total} rows > capacity {ep.capacity}")
+            ctx.mark_dirty(out)  # written in place and returned
+        grouped_gemm(1, a, weight, out, N, K, plan)
+        ctx.save_for_backward(a)
+        ctx.weight, ctx.plan, ctx.dgrad_out = weight, plan, dgrad_out
+        weight._pb_direct_grad = True
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (a,) = ctx.saved_tensors
+        weight, plan = ctx.weight, ctx.plan
+        G, N, K = weight.shape
+        dy = dy.contiguous()
+        da = None
+        if ctx.needs_input_grad[0]:
+            da = ctx.dgrad_out if ctx.dgrad_out is not None else torch.empty_like(a)
+            grouped_gemm(1, dy, weight, da, K, N, plan, b_mn=True)
+
+        def wgrad():
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                grouped_gemm(2, dy, a, mg, K, a.shape[0], plan, accumulate=True)
+            else:
+                dw = torch.empty(G, N, K, dtype=torch.bfloat16, device=a.device)
+                grouped_gemm(2, dy, a, dw, K, a.shape[0], plan)
+                pf._accumulate_param_grad(weight, dw)
+
+        if weight.requires_grad:
+            _run_or_defer(wgrad)
+        return da, None, None, None, None
 
 
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, plan: _Plan):
         ep = plan.ep
-        ep.dispatch(x.contiguous(), plan.expert, plan.slot, plan.dst_base, None, plan.experts_per_rank)
+        ep.dispatch(x.contiguous(), plan, None)
         ctx.plan = plan
         ctx.T = x.shape[0]
-        return ep.recv_rows(plan.recv_total).clone()
+        # the receive buffer is shared by all layers: the rows are copied out (they are also what the expert
+        # weight gradients need later)
+        return ep.recv_rows().clone()
 
     @staticmethod
     def backward(ctx, d_recv):
         plan, ep = ctx.plan, ctx.plan.ep
-        ep.y_rows(plan.recv_total).copy_(d_recv)
+        ybuf = ep.y_rows()
+        if d_recv.data_ptr() != ybuf.data_ptr():
+            ybuf.copy_(d_recv)
         dx = torch.empty(ctx.T, ep.hidden, dtype=torch.bfloat16, device=d_recv.device)
-        ep.combine(dx, plan.expert, plan.slot, plan.dst_base, None, None, plan.experts_per_rank)
+        ep.combine(dx, plan, None, None)
         return dx, None
 
 
@@ -144,11 +248,13 @@ class _CombineFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y_local, weight, plan: _Plan, T: int):
         ep = plan.ep
-        ep.y_rows(plan.recv_total).copy_(y_local)
+        ybuf = ep.y_rows()
+        if y_local.data_ptr() != ybuf.data_ptr():
+            ybuf.copy_(y_local)
         out = torch.empty(T, ep.hidden, dtype=torch.bfloat16, device=y_local.device)
         save = torch.empty(T * ep.top_k, ep.hidden, dtype=torch.bfloat16, device=y_local.device)
         w = weight.reshape(-1).float().contiguous()
-        ep.combine(out, plan.expert, plan.slot, plan.dst_base, w, save, plan.experts_per_rank)
+        ep.combine(out, plan, w, save)
         ctx.save_for_backward(save, w)
         ctx.plan = plan
         ctx.wshape = weight.shape
@@ -165,8 +271,8 @@ class _CombineFn(torch.autograd.Function):
         _lib.check(_lib.lib().pb_moe_rowdot(_lib.ptr(dout), _lib.ptr(save), _lib.ptr(dots), _lib.c_int(T),
                                             _lib.c_int(ep.top_k), _lib.c_int(ep.hidden), _lib.stream_ptr()),
                    "pb_moe_rowdot")
-        ep.dispatch(dout, plan.expert, plan.slot, plan.dst_base, w, plan.experts_per_rank)
-        dy_local = ep.recv_rows(plan.recv_total).clone()
+        ep.dispatch(dout, plan, w)
+        dy_local = ep.recv_rows().clone()
         return dy_local, dots.view(ctx.wshape).to(ctx.wdtype), None, None
 
 
@@ -188,7 +294,8 @@ class _AuxLossInject(torch.autograd.Function):
 
 class MoEFeedForward(nn.Module):
     """Top-k routed SwiGLU experts. ``n_experts`` in total, this rank holds ``n_experts / ep_size`` of them
-    (expert ``e`` lives on rank ``e // experts_per_rank``). Input/output: ``[T, dim]``."""
+    (expert ``e`` lives on rank ``e // experts_per_rank``) as two stacked parameters ``w_gate_up [local, 2 ffn, dim]``
+    and ``w_down [local, dim, ffn]``. Input/output: ``[T, dim]``."""
 
     def __init__(self, dim: int, ffn_dim: int, n_experts: int, top_k: int = 2, ep: Optional[EPContext] = None,
                  ep_size: int = 1, ep_rank: int = 0, aux_coef: float = 0.01, init_std: float = 0.02, device=None,
@@ -197,27 +304,28 @@ class MoEFeedForward(nn.Module):
         assert n_experts % ep_size == 0
         self.dim, self.ffn_dim, self.n_experts, self.top_k = dim, ffn_dim, n_experts, top_k
         self.ep, self.ep_size, self.ep_rank, self.aux_coef = ep, ep_size, ep_rank, aux_coef
-        self.local_experts = list(range(ep_rank * (n_experts // ep_size), (ep_rank + 1) * (n_experts // ep_size)))
+        n_local = n_experts // ep_size
+        self.local_experts = list(range(ep_rank * n_local, (ep_rank + 1) * n_local))
+        if ep is not None and (ep.n_experts != n_experts or ep.top_k != top_k or ep.hidden != dim):
+            raise ValueError("the expert-parallel context was built for another layer shape")
         # the router GEMM needs a 16-byte row pitch on its output: rows beyond n_experts are padding (zero, unused)
         e_pad = (n_experts + 7) // 8 * 8
         self.router = nn.Parameter(torch.zeros(e_pad, dim, device=device, dtype=dtype))
+        self.w_gate_up = nn.Parameter(torch.empty(n_local, 2 * ffn_dim, dim, device=device, dtype=dtype))
+        self.w_down = nn.Parameter(torch.empty(n_local, dim, ffn_dim, device=device, dtype=dtype))
         with torch.no_grad():
             self.router[:n_experts].normal_(std=init_std)
-        self.w_gate_up = nn.ParameterDict()
-        self.w_down = nn.ParameterDict()
-        for e in self.local_experts:
-            gu = nn.Parameter(torch.empty(2 * ffn_dim, dim, device=device, dtype=dtype))
-            dn = nn.Parameter(torch.empty(dim, ffn_dim, device=device, dtype=dtype))
-            nn.init.normal_(gu, std=init_std)
-            nn.init.normal_(dn, std=init_std)
-            self.w_gate_up[str(e)] = gu
-            self.w_down[str(e)] = dn
+            self.w_gate_up.normal_(std=init_std)
+            self.w_down.normal_(std=init_std)
         self.last_aux_loss: Optional[torch.Tensor] = None
 
-    def _route(self, x):
-        logits = pf.linear(x, self.router)[:, : self.n_experts].float()
+    def _route_reference(self, x):
+        logits = F.linear(x, self.router)[:, : self.n_experts].float()
         probs = logits.softmax(-1)
-        topw, topi = probs.topk(self.top_k, dim=-1)
+        # a stable sort breaks ties towards the lower expert index, as the router kernel does
+        order = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, : self.top_k]
+        topi = order
+        topw = probs.gather(-1, topi)
         topw = topw / topw.sum(-1, keepdim=True)
         # load-balance loss: E * sum_e (share of assignments to e) * (mean router probability of e)
         share = torch.zeros(self.n_experts, device=x.device, dtype=torch.float32)
@@ -228,35 +336,35 @@ class MoEFeedForward(nn.Module):
 
     def forward(self, x):
         T = x.shape[0]
-        topw, topi, aux = self._route(x)
-        self.last_aux_loss = aux.detach()
-        if self.aux_coef:
-            x = _AuxLossInject.apply(x, aux * self.aux_coef)
         if self.ep is not None and x.is_cuda and x.dtype == torch.bfloat16:
-            plan = _Plan(self.ep, topi.reshape(-1).to(torch.int32).contiguous(), self.n_experts)
+            plan = _Plan(self.ep, T)
+            logits = pf.linear(x, self.router)
+            topw, aux = _RouteFn.apply(logits, plan, self.n_experts, self.top_k)
+            self.last_aux_loss = aux.detach()
+            if self.aux_coef:
+                x = _AuxLossInject.apply(x, aux * self.aux_coef)
             rows = _DispatchFn.apply(x, plan)
-            outs, start = [], 0
-            for e, n in zip(self.local_experts, plan.local_totals):
-                xe = rows[start : start + n]
-                start += n
-                if n == 0:
-                    outs.append(xe)
-                    continue
-                h = pf.swiglu(pf.linear(xe, self.w_gate_up[str(e)]))
-                outs.append(pf.linear(h, self.w_down[str(e)]))
-            y_local = torch.cat(outs, 0) if len(outs) > 1 else outs[0]
-            return _CombineFn.apply(y_local, topw.to(x.dtype), plan, T)
+            ybuf = self.ep.y_rows()
+            # the input gradient of the first projection goes straight into the buffer the backward's combine
+            # reads, the output of the second one into the buffer the forward's combine reads
+            h = pf.swiglu(_GroupedLinearFn.apply(rows, self.w_gate_up, plan, None, ybuf))
+            y_local = _GroupedLinearFn.apply(h, self.w_down, plan, ybuf, None)
+            return _CombineFn.apply(y_local, topw, plan, T)
         # dense reference path (one rank holds every expert): plain PyTorch statement of the same layer
         if self.ep_size != 1:
             raise RuntimeError("the reference MoE path needs all experts on one rank")
+        topw, topi, aux = self._route_reference(x)
+        self.last_aux_loss = aux.detach()
+        if self.aux_coef:
+            x = _AuxLossInject.apply(x, aux * self.aux_coef)
         out = torch.zeros_like(x, dtype=torch.float32)
-        for e in self.local_experts:
+        for i, e in enumerate(self.local_experts):
             mask = topi == e
             tok = mask.any(-1).nonzero(as_tuple=True)[0]
             if tok.numel() == 0:
                 continue
             w = (topw * mask).sum(-1)[tok]
-            h = pf.swiglu(pf.linear(x[tok], self.w_gate_up[str(e)]))
-            y = pf.linear(h, self.w_down[str(e)])
+            g, u = F.linear(x[tok], self.w_gate_up[i]).chunk(2, dim=-1)
+            y = F.linear(F.silu(g) * u, self.w_down[i])
             out.index_add_(0, tok, y.float() * w[:, None].float())
         return out.to(x.dtype)

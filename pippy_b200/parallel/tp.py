@@ -117,14 +117,16 @@ class _ColumnParallelFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, weight, tp: TPContext):
         y, _ = tp.ag_gemm(x_shard, weight)
-        ctx.save_for_backward(x_shard, weight)
+        ctx.save_for_backward(x_shard)
+        ctx.weight = weight  # parameters ride on ctx: saved-tensor hooks (checkpointing) would hand back a stand-in
         ctx.tp = tp
         weight._pb_direct_grad = True
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x_shard, weight = ctx.saved_tensors
+        (x_shard,) = ctx.saved_tensors
+        weight = ctx.weight
         tp = ctx.tp
         dy = dy.contiguous()
         dx_shard = tp.gemm_rs(dy, weight, b_mn=True)  # [T, N_local] . [N_local, K] -> rows scattered
@@ -141,7 +143,8 @@ class _RowParallelFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, residual_shard, tp: TPContext):
         out = tp.gemm_rs(x, weight, residual=residual_shard)
-        ctx.save_for_backward(x, weight)
+        ctx.save_for_backward(x)
+        ctx.weight = weight
         ctx.tp = tp
         ctx.has_res = residual_shard is not None
         weight._pb_direct_grad = True
@@ -149,7 +152,8 @@ class _RowParallelFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout_shard):
-        x, weight = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
+        weight = ctx.weight
         tp = ctx.tp
         dout_shard = dout_shard.contiguous()
         dx, gathered = tp.ag_gemm(dout_shard, weight, b_mn=True)  # gather(dOut) . W -> [T, K_local]

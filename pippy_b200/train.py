@@ -234,6 +234,7 @@ def build_mixtral_pipeline(
     weight_decay: float = 0.1,
     seed: int = 0,
     record_timing: bool = False,
+    capacity_factor: float = 1.5,
 ) -> Pipeline:
     """Mixtral stages for a PP x EP layout. ``global_batch`` is the batch of ONE expert-parallel rank (EP ranks are
     data-parallel replicas for the dense layers): dense gradients are averaged over ``ep_group`` with the fused
@@ -250,8 +251,9 @@ def build_mixtral_pipeline(
     num_stages = pp_size * virtual_stages
     mb = global_batch // n_microbatches
     ep = None
-    if ep_size > 1 and device.type == "cuda":
-        ep = EPContext(ep_group, max_tokens=mb * seq_len, hidden=cfg.dim, top_k=cfg.top_k, device=device)
+    if device.type == "cuda" and (ep_size > 1 or ep_group is not None or not dist.is_initialized()):
+        ep = EPContext(ep_group, max_tokens=mb * seq_len, hidden=cfg.dim, top_k=cfg.top_k, n_experts=cfg.n_experts,
+                       device=device, capacity_factor=capacity_factor)
     stages: List[ManualPipelineStage] = []
     dense, experts = [], []
     for k in range(virtual_stages):

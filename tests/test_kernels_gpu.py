@@ -363,3 +363,70 @@ def test_llama_activation_checkpointing_same_gradients(schedule):
     for n, g in grads[False].items():
         assert g.abs().max().item() > 0, n
         assert _rel(grads[True][n], g) < 1e-3, n
+
+
+def test_moe_router_kernels():
+    """softmax / top-k / normalised weights / load-balance loss / positions, and the logit gradient, against the
+    plain PyTorch statement."""
+    from pippy_b200.parallel.ep import EPContext, _Plan, _RouteFn
+
+    T, E, k, H = 1000, 8, 2, 64
+    ep = EPContext(None, max_tokens=T, hidden=H, top_k=k, n_experts=E)
+    logits = _bf16(T, E, scale=1.5).requires_grad_()
+    plan = _Plan(ep, T)
+    topw, aux = _RouteFn.apply(logits, plan, E, k)
+    gw = torch.randn(T, k, device="cuda")
+    ((topw * gw).sum() + 0.37 * aux).backward()
+
+    lf = logits.detach().float().requires_grad_()
+    probs = lf.softmax(-1)
+    ri = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :k]  # ties: lower index first
+    rw = probs.gather(-1, ri)
+    rwn = rw / rw.sum(-1, keepdim=True)
+    share = torch.bincount(ri.reshape(-1), minlength=E).float() / (T * k)
+    raux = E * (share * probs.mean(0)).sum()
+    ((rwn * gw).sum() + 0.37 * raux).backward()
+    assert torch.equal(plan.expert.view(T, k).long(), ri)
+    torch.testing.assert_close(topw, rwn, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(aux, raux, rtol=1e-5, atol=1e-6)
+    assert torch.equal(plan.counts.long(), torch.bincount(ri.reshape(-1), minlength=E))
+    # positions: assignment (t, j) is the n-th token (in token order) that chose its expert
+    flat = ri.reshape(-1)
+    want = torch.empty_like(flat)
+    for e in range(E):
+        idx = (flat == e).nonzero(as_tuple=True)[0]
+        want[idx] = torch.arange(idx.numel(), device="cuda")
+    assert torch.equal(plan.slot.long(), want)
+    assert _rel(logits.grad, lf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("T", [384, 1500])
+def test_moe_layer_one_rank_against_dense(T):
+    """The whole expert-parallel layer (route, dispatch, grouped GEMMs, combine and their backward) with an
+    expert-parallel group of one rank, against the dense PyTorch statement of the layer."""
+    from pippy_b200.parallel.ep import EPContext, MoEFeedForward
+
+    H, Fd, E, k = 256, 512, 4, 2
+    ep = EPContext(None, max_tokens=T, hidden=H, top_k=k, n_experts=E, capacity_factor=1.0)
+    torch.manual_seed(5)
+    dense = MoEFeedForward(H, Fd, E, k, None, 1, 0, aux_coef=0.01, device="cuda", dtype=torch.bfloat16)
+    fused = MoEFeedForward(H, Fd, E, k, ep, 1, 0, aux_coef=0.01, device="cuda", dtype=torch.bfloat16)
+    fused.load_state_dict(dense.state_dict())
+    for it in range(2):  # the second pass reuses buffers and flags
+        x = _bf16(T, H)
+        dy = _bf16(T, H)
+        xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+        for m in (dense, fused):
+            for p in m.parameters():
+                p.grad = None
+        out = fused(xa)
+        out.backward(dy)
+        ref = dense(xb)
+        ref.backward(dy)
+        torch.cuda.synchronize()
+        assert _rel(out, ref) < 2e-2, ("out", it)
+        assert _rel(xa.grad, xb.grad) < 2e-2, ("dx", it)
+        assert _rel(fused.router.grad[:E], dense.router.grad[:E]) < 3e-2, ("drouter", it)
+        assert _rel(fused.w_down.grad, dense.w_down.grad) < 2e-2, ("dWdown", it)
+        assert _rel(fused.w_gate_up.grad, dense.w_gate_up.grad) < 2e-2, ("dWgu", it)
+        assert abs(float(fused.last_aux_loss) - float(dense.last_aux_loss)) < 1e-3
