@@ -100,6 +100,10 @@ def _pippy_blocks(world: int) -> bool:
 def main(args) -> None:
     ref_path = os.path.join(HERE, "_ref")
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if getattr(args, "config", "llama7b-pp") != "llama7b-pp":
+        _unavailable(f"the reference arm covers the headline config (llama7b-pp) only; {args.config} composes the "
+                     "pipeline with data, tensor or expert parallelism, which the reference leaves to other libraries")
+        return
     system = os.environ.get("PIPPY_REF_SYSTEM") or ("torch.distributed.pipelining" if _pippy_blocks(world) else "pippy")
     if system == "pippy":
         if not os.path.isdir(os.path.join(ref_path, "pippy")):

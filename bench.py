@@ -38,15 +38,31 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--schedule", default=None, help="interleaved_1f1b | zero_bubble | zbv | 1f1b | gpipe | looped_bfs")
+    ap.add_argument("--config", default="llama7b-pp",
+                    help="llama7b-pp (the headline config, PP = number of GPUs) | gpt2-pp4dp2 | llama13b-tp4pp2 | "
+                         "mixtral-pp2ep4 (the other composed configs; on fewer than 8 GPUs the pipeline dimension "
+                         "shrinks first)")
     ap.add_argument("--model", default="llama2-7b", help="llama2-7b | llama-small (for quick checks only)")
-    ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--seq", type=int, default=4096)
-    ap.add_argument("--microbatches", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=None, help="global batch (default: the config's)")
+    ap.add_argument("--seq", type=int, default=None)
+    ap.add_argument("--microbatches", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (quick checks only)")
     ap.add_argument("--virtual", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sm-reserve", type=int, default=None,
                     help="SMs kept out of the GEMM grid for communication kernels (default: 0 on 1 GPU, 8 otherwise)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    defaults = {  # global batch, sequence length, microbatches per pipeline replica
+        "llama7b-pp": (64, 4096, 32), "gpt2-pp4dp2": (64, 1024, 16), "llama13b-tp4pp2": (32, 4096, 16),
+        "mixtral-pp2ep4": (32, 4096, 8),
+    }
+    if args.config not in defaults:
+        raise SystemExit(f"unknown config {args.config}")
+    b, sq, mbs = defaults[args.config]
+    args.batch = b if args.batch is None else args.batch
+    args.seq = sq if args.seq is None else args.seq
+    args.microbatches = mbs if args.microbatches is None else args.microbatches
+    return args
 
 
 class ClockSampler:
@@ -119,6 +135,85 @@ def model_config(name: str):
     raise SystemExit(f"unknown model {name}")
 
 
+def build_job(args, world: int, device):
+    """Builds this rank's pipeline for ``args.config``.  Returns ``(pipe, info)``; ``info`` says which slice of the
+    global batch this rank feeds, the model's training FLOPs per token and how the job is laid out."""
+    import torch.distributed as dist
+
+    from pippy_b200 import train
+    from pippy_b200.parallel.mesh import init_mesh
+
+    if args.config == "llama7b-pp":
+        cfg, model_desc = model_config(args.model)
+        if args.layers:
+            cfg.n_layers = args.layers
+        schedule = args.schedule or ("interleaved_1f1b" if world == 1 else "zero_bubble")
+        virtual = 1 if schedule in ("gpipe", "1f1b") else args.virtual
+        pipe = train.build_llama_pipeline(cfg, args.batch, args.seq, args.microbatches, device, schedule=schedule,
+                                          virtual_stages=virtual, lr=3e-4, weight_decay=0.1)
+        return pipe, dict(cfg=cfg, model=model_desc, schedule=schedule, virtual=virtual, replica=0, replicas=1,
+                          parallelism=f"pp{world}" + (f"x{virtual}v" if virtual > 1 else ""),
+                          flops_per_token=cfg.flops_per_token(args.seq), vocab=cfg.vocab_size)
+    if world == 1:
+        raise SystemExit(f"--config {args.config} composes parallel dimensions: run it on 2 or more GPUs")
+    if args.config == "gpt2-pp4dp2":
+        from pippy_b200.models.gpt2 import GPT2Config
+
+        dp = 2 if world % 2 == 0 else 1
+        pp = world // dp
+        mesh = init_mesh(pp_size=pp, dp_size=dp)
+        cfg = GPT2Config.small()
+        if args.layers:
+            cfg.n_layers = args.layers
+        schedule = args.schedule or "1f1b"
+        virtual = 1 if schedule in ("gpipe", "1f1b") else args.virtual
+        pipe = train.build_gpt2_pipeline(cfg, args.batch // dp, args.seq, args.microbatches, device, schedule=schedule,
+                                         virtual_stages=virtual, group=mesh.pp_group, dp_group=mesh.dp_group)
+        d, L, V = cfg.dim, cfg.n_layers, cfg.vocab_size
+        flops = 6.0 * (L * 12 * d * d + V * d) + 3.0 * L * 2 * args.seq * d
+        return pipe, dict(cfg=cfg, model=f"GPT-2 small ({L}L, d{d}, vocab {V}, tied embedding / LM head)",
+                          schedule=schedule, virtual=virtual, replica=mesh.dp_rank, replicas=dp,
+                          parallelism=f"pp{pp}xdp{dp}", flops_per_token=flops, vocab=V)
+    if args.config == "llama13b-tp4pp2":
+        from pippy_b200.models.llama import LlamaConfig
+
+        tp = 4 if world % 4 == 0 else 2
+        pp = world // tp
+        mesh = init_mesh(pp_size=pp, tp_size=tp)
+        cfg = LlamaConfig.llama2_13b()
+        if args.layers:
+            cfg.n_layers = args.layers
+        schedule = args.schedule or "1f1b"
+        pipe = train.build_llama_tp_pipeline(cfg, args.batch, args.seq, args.microbatches, device, schedule=schedule,
+                                             pp_group=mesh.pp_group, tp_group=mesh.tp_group)
+        return pipe, dict(cfg=cfg, model=f"Llama-2-13B shape ({cfg.n_layers}L, d5120, 40h, ffn 13824, vocab 32000)",
+                          schedule=schedule, virtual=1, replica=0, replicas=1,
+                          parallelism=f"tp{tp}xpp{pp} (sequence-parallel activations)",
+                          flops_per_token=cfg.flops_per_token(args.seq), vocab=cfg.vocab_size)
+    if args.config == "mixtral-pp2ep4":
+        from pippy_b200.models.mixtral import MixtralConfig
+
+        ep = 4 if world % 4 == 0 else 2
+        pp = world // ep
+        mesh = init_mesh(pp_size=pp, tp_size=ep)  # the mesh's fastest axis carries the experts
+        cfg = MixtralConfig.mixtral_16l()
+        if args.layers:
+            cfg.n_layers = args.layers
+        schedule = args.schedule or ("1f1b" if pp > 1 else "gpipe")
+        pipe = train.build_mixtral_pipeline(cfg, args.batch // ep, args.seq, args.microbatches, device,
+                                            schedule=schedule, pp_group=mesh.pp_group, ep_group=mesh.tp_group)
+        d, hd = cfg.dim, cfg.head_dim
+        attn_mm = d * (cfg.n_heads + 2 * cfg.kv_heads) * hd + d * d
+        moe_mm = cfg.top_k * 3 * d * cfg.ffn_dim + d * cfg.n_experts
+        flops = 6.0 * (cfg.n_layers * (attn_mm + moe_mm) + cfg.vocab_size * d) + 3.0 * cfg.n_layers * 2 * args.seq * d
+        return pipe, dict(cfg=cfg, model=f"Mixtral shape ({cfg.n_layers}L, d4096, 32q/8kv heads, 8 experts of ffn 14336, "
+                                         "top-2)",
+                          schedule=schedule, virtual=1, replica=mesh.tp_rank, replicas=ep,
+                          parallelism=f"pp{pp}xep{ep} (expert-parallel ranks are data-parallel for the dense layers)",
+                          flops_per_token=flops, vocab=cfg.vocab_size)
+    raise SystemExit(f"unknown config {args.config}")
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
@@ -132,7 +227,6 @@ def main() -> None:
     import torch.distributed as dist
 
     from pippy_b200.ops import _lib
-    from pippy_b200.train import build_llama_pipeline
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -150,25 +244,22 @@ def main() -> None:
 
     sm_reserve = args.sm_reserve if args.sm_reserve is not None else (0 if world == 1 else 8)
     set_sm_reserve(sm_reserve)
-    cfg, model_desc = model_config(args.model)
-    schedule = args.schedule or ("interleaved_1f1b" if world == 1 else "zero_bubble")
-    virtual = args.virtual
-    if schedule in ("gpipe", "1f1b"):
-        virtual = 1
-    pipe = build_llama_pipeline(
-        cfg, args.batch, args.seq, args.microbatches, device, schedule=schedule, virtual_stages=virtual,
-        lr=3e-4, weight_decay=0.1,
-    )
+    pipe, info = build_job(args, world, device)
+    schedule, virtual, model_desc = info["schedule"], info["virtual"], info["model"]
 
-    # synthetic data of the named shape: uniform token ids, labels = ids shifted by one
+    # synthetic data of the named shape: uniform token ids, labels = ids shifted by one; a data- (or expert-)
+    # parallel replica feeds its own slice of the global batch
     g = torch.Generator().manual_seed(1234)
     n_sets = 2
-    host_ids = [torch.randint(0, cfg.vocab_size, (args.batch, args.seq), generator=g).pin_memory() for _ in range(n_sets)]
-    host_lbl = []
-    for ids in host_ids:
+    per_replica = args.batch // info["replicas"]
+    rows = slice(info["replica"] * per_replica, (info["replica"] + 1) * per_replica)
+    host_ids, host_lbl = [], []
+    for _ in range(n_sets):
+        ids = torch.randint(0, info["vocab"], (args.batch, args.seq), generator=g)
         lbl = torch.roll(ids, -1, dims=1)
         lbl[:, -1] = -100
-        host_lbl.append(lbl.pin_memory())
+        host_ids.append(ids[rows].contiguous().pin_memory())
+        host_lbl.append(lbl[rows].contiguous().pin_memory())
     dev_ids = [t.to(device) for t in host_ids] if pipe.holds_first else [None] * n_sets
     dev_lbl = [t.to(device) for t in host_lbl] if pipe.holds_last else [None] * n_sets
 
@@ -270,8 +361,8 @@ def main() -> None:
     # ---------------------------------------------------------------- same stages under interleaved 1F1B (the
     # schedule the reference arm runs), so that the runtime's and the schedule's share of a gain can be told apart
     like_for_like = None
-    if world > 1 and schedule != "interleaved_1f1b" and args.microbatches % world == 0 and virtual > 1 \
-            and schedule != "zbv":
+    if args.config == "llama7b-pp" and world > 1 and schedule != "interleaved_1f1b" \
+            and args.microbatches % world == 0 and virtual > 1 and schedule != "zbv":
         from pippy_b200.models.llama import causal_lm_loss
         from pippy_b200.schedules import ScheduleInterleaved1F1B
 
@@ -297,7 +388,7 @@ def main() -> None:
         tokens = args.batch * args.seq * args.steps
         value = tokens / (ms_total * 1e-3)
         ms_per_step = ms_total / args.steps
-        tflops = cfg.flops_per_token(args.seq) * value / 1e12
+        tflops = info["flops_per_token"] * value / 1e12
         out = {
             "metric": "tokens/sec (whole job, device-timed, max over ranks)",
             "value": value,
@@ -317,7 +408,8 @@ def main() -> None:
                 "global_batch": args.batch,
                 "seq_len": args.seq,
                 "microbatches": args.microbatches,
-                "parallelism": f"pp{world}" + (f"x{virtual}v" if virtual > 1 else ""),
+                "name": args.config,
+                "parallelism": info["parallelism"],
                 "schedule": schedule,
                 "sm_reserve": sm_reserve,
                 "optimizer": "AdamW lr 3e-4 (fused, fp32 moments, fp32 gradient accumulation)",

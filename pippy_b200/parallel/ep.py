@@ -180,20 +180,15 @@ def grouped_gemm(mode: int, a, b, out, n, k_dim, plan: _Plan, b_mn: bool = False
 
 
 class _GroupedLinearFn(torch.autograd.Function):
-    """``y[r] = a[r] @ weight[g].T`` for the rows r of local expert g; ``weight`` is ``[G, N, K]``.  ``out`` /
-    ``dgrad_out`` let the caller place the result (and the input gradient) in a buffer of its choice, e.g. the
-    peer-mapped buffer the combine kernel reads."""
+    """``y[r] = a[r] @ weight[g].T`` for the rows r of local expert g; ``weight`` is ``[G, N, K]``."""
 
     @staticmethod
-    def forward(ctx, a, weight, plan: _Plan, out, dgrad_out):
+    def forward(ctx, a, weight, plan: _Plan):
         G, N, K = weight.shape
-        if out is None:
-            out = torch.empty(a.shape[0], N, dtype=torch.bfloat16, device=a.device)
-        else:
-            ctx.mark_dirty(out)  # written in place and returned
+        out = torch.empty(a.shape[0], N, dtype=torch.bfloat16, device=a.device)
         grouped_gemm(1, a, weight, out, N, K, plan)
         ctx.save_for_backward(a)
-        ctx.weight, ctx.plan, ctx.dgrad_out = weight, plan, dgrad_out
+        ctx.weight, ctx.plan = weight, plan  # the parameter rides on ctx (see ops.functional._LinearFn)
         weight._pb_direct_grad = True
         return out
 
@@ -205,7 +200,7 @@ class _GroupedLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         da = None
         if ctx.needs_input_grad[0]:
-            da = ctx.dgrad_out if ctx.dgrad_out is not None else torch.empty_like(a)
+            da = torch.empty_like(a)
             grouped_gemm(1, dy, weight, da, K, N, plan, b_mn=True)
 
         def wgrad():
@@ -219,7 +214,7 @@ class _GroupedLinearFn(torch.autograd.Function):
 
         if weight.requires_grad:
             _run_or_defer(wgrad)
-        return da, None, None, None, None
+        return da, None, None
 
 
 class _DispatchFn(torch.autograd.Function):
@@ -236,9 +231,7 @@ class _DispatchFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_recv):
         plan, ep = ctx.plan, ctx.plan.ep
-        ybuf = ep.y_rows()
-        if d_recv.data_ptr() != ybuf.data_ptr():
-            ybuf.copy_(d_recv)
+        ep.y_rows().copy_(d_recv)  # into the peer-mapped buffer the owners of the tokens pull from
         dx = torch.empty(ctx.T, ep.hidden, dtype=torch.bfloat16, device=d_recv.device)
         ep.combine(dx, plan, None, None)
         return dx, None
@@ -248,9 +241,7 @@ class _CombineFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y_local, weight, plan: _Plan, T: int):
         ep = plan.ep
-        ybuf = ep.y_rows()
-        if y_local.data_ptr() != ybuf.data_ptr():
-            ybuf.copy_(y_local)
+        ep.y_rows().copy_(y_local)  # into the peer-mapped buffer the owners of the tokens pull from
         out = torch.empty(T, ep.hidden, dtype=torch.bfloat16, device=y_local.device)
         save = torch.empty(T * ep.top_k, ep.hidden, dtype=torch.bfloat16, device=y_local.device)
         w = weight.reshape(-1).float().contiguous()
@@ -344,11 +335,8 @@ class MoEFeedForward(nn.Module):
             if self.aux_coef:
                 x = _AuxLossInject.apply(x, aux * self.aux_coef)
             rows = _DispatchFn.apply(x, plan)
-            ybuf = self.ep.y_rows()
-            # the input gradient of the first projection goes straight into the buffer the backward's combine
-            # reads, the output of the second one into the buffer the forward's combine reads
-            h = pf.swiglu(_GroupedLinearFn.apply(rows, self.w_gate_up, plan, None, ybuf))
-            y_local = _GroupedLinearFn.apply(h, self.w_down, plan, ybuf, None)
+            h = pf.swiglu(_GroupedLinearFn.apply(rows, self.w_gate_up, plan))
+            y_local = _GroupedLinearFn.apply(h, self.w_down, plan)
             return _CombineFn.apply(y_local, topw, plan, T)
         # dense reference path (one rank holds every expert): plain PyTorch statement of the same layer
         if self.ep_size != 1:

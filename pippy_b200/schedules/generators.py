@@ -200,6 +200,193 @@ def zero_bubble(
     return out
 
 
+def zero_bubble_costed(
+    P: int,
+    v: int,
+    n_mb: int,
+    cost: Dict[int, tuple],
+    comm_latency: float = 0.0,
+    max_pending_w: Optional[int] = None,
+    extra_in_flight: int = 0,
+    placement: Optional[Dict[int, int]] = None,
+    return_makespan: bool = False,
+):
+    """Zero-bubble order from MEASURED per-stage costs: ``cost[s] = (forward, input-gradient, weight-gradient)``
+    durations of one microbatch on stage ``s``, in any common unit.  Same policy as :func:`zero_bubble` (a ready I
+    first, then a forward while the in-flight limit allows, weight gradients in the gaps), but on a continuous
+    event-driven timeline, so that a heavier stage (the one with the LM head and the loss) and an I : W ratio that
+    differs from the 3 : 2 guess shift the order instead of showing up as idle time.  A value produced on another
+    rank becomes usable ``comm_latency`` after its producer ends.  With ``placement`` (stage -> rank) the forward and
+    input-gradient orders are per stage, nearest the loss first, as in :func:`zero_bubble_placed`."""
+    S = P * v if placement is None else len(placement)
+    where = (lambda s: s % P) if placement is None else (lambda s: placement[s])
+    if placement is None and v > 1 and n_mb % P != 0:
+        raise ValueError(
+            f"interleaved zero-bubble requires the number of microbatches ({n_mb}) to be a multiple of the "
+            f"pipeline group size ({P})"
+        )
+    if sorted(cost) != list(range(S)):
+        raise ValueError(f"cost must give (F, I, W) for stages 0..{S - 1}")
+    if max_pending_w is None:
+        max_pending_w = max(2 * P, 4)
+    local = {r: sorted((s for s in range(S) if where(s) == r), reverse=True) for r in range(P)}
+    wrap = placement is None
+    if wrap:
+        f_seq, i_seq = {}, {}
+        for r in range(P):
+            f_seq[r], i_seq[r] = _interleaved_orders(P, v, n_mb, r)
+        fp = {r: 0 for r in range(P)}
+        ip = {r: 0 for r in range(P)}
+        cap_rank = {r: (v - 1) * P + (P - 1 - r) + 1 + extra_in_flight for r in range(P)}
+        in_flight_rank = {r: 0 for r in range(P)}
+    else:
+        next_f = {s: 0 for s in range(S)}
+        next_i = {s: 0 for s in range(S)}
+        cap_stage = {s: min(n_mb, S - s + extra_in_flight) for s in range(S)}
+        in_flight_stage = {s: 0 for s in range(S)}
+    wq: Dict[int, List] = {r: [] for r in range(P)}
+    free_at = {r: 0.0 for r in range(P)}
+    left = {r: 3 * n_mb * len(local[r]) for r in range(P)}
+    finish: Dict[tuple, float] = {}
+    out: Schedule = {r: [] for r in range(P)}
+    INF = float("inf")
+
+    def ready_at(key, consumer_rank):
+        t = finish.get(key)
+        if t is None:
+            return INF
+        return t + (comm_latency if where(key[0]) != consumer_rank else 0.0)
+
+    def f_ready(s, m, r):
+        return 0.0 if s == 0 else ready_at((s - 1, "F", m), r)
+
+    def i_ready(s, m, r):
+        t = ready_at((s, "F", m), r)
+        return t if s == S - 1 else max(t, ready_at((s + 1, "I", m), r))
+
+    blocked = set()  # ranks waiting for a producer that nobody has scheduled yet
+    while any(left.values()):
+        runnable = [q for q in range(P) if left[q] and q not in blocked]
+        if not runnable:
+            # every rank waits for a producer that no rank may start (the two limits can block each other)
+            raise RuntimeError("zero-bubble list scheduling is stuck: the in-flight and pending limits deadlock")
+        r = min(runnable, key=lambda q: (free_at[q], q))
+        t = free_at[r]
+        choice = None
+        waits = []  # times at which something this rank could do becomes ready
+        # 1. a ready input-gradient pass
+        if wrap:
+            if ip[r] < len(i_seq[r]):
+                s, m = i_seq[r][ip[r]]
+                ta = i_ready(s, m, r)
+                if ta <= t:
+                    choice = ("I", s, m)
+                else:
+                    waits.append(ta)
+        else:
+            cands = []
+            for s in local[r]:
+                m = next_i[s]
+                if m < n_mb:
+                    ta = i_ready(s, m, r)
+                    if ta <= t:
+                        cands.append((m, -s, s))
+                    else:
+                        waits.append(ta)
+            if cands:
+                m, _, s = min(cands)
+                choice = ("I", s, m)
+        # 2. too many parked weight gradients
+        if choice is None and len(wq[r]) > max_pending_w:
+            choice = ("W",) + wq[r][0]
+        # 3. a ready forward within the in-flight limit
+        if choice is None:
+            if wrap:
+                if fp[r] < len(f_seq[r]) and in_flight_rank[r] < cap_rank[r]:
+                    s, m = f_seq[r][fp[r]]
+                    ta = f_ready(s, m, r)
+                    if ta <= t:
+                        choice = ("F", s, m)
+                    else:
+                        waits.append(ta)
+            else:
+                for s in local[r]:
+                    m = next_f[s]
+                    if m < n_mb and in_flight_stage[s] < cap_stage[s]:
+                        ta = f_ready(s, m, r)
+                        if ta <= t:
+                            choice = ("F", s, m)
+                            break
+                        waits.append(ta)
+        # 4. fill the gap with the oldest parked weight gradient
+        if choice is None and wq[r]:
+            choice = ("W",) + wq[r][0]
+        if choice is None:
+            # idle until the next known arrival; with none known, sleep until some rank schedules an action (only
+            # that can make one of this rank's producers known)
+            nxt = [w for w in waits if t < w < INF]
+            if nxt:
+                free_at[r] = min(nxt)
+            else:
+                blocked.add(r)
+            continue
+        for q in blocked:
+            free_at[q] = max(free_at[q], t)
+        blocked.clear()
+        kind, s, m = choice
+        cf, ci, cw = cost[s]
+        if kind == "F":
+            if wrap:
+                fp[r] += 1
+                in_flight_rank[r] += 1
+            else:
+                next_f[s] += 1
+                in_flight_stage[s] += 1
+            dur = cf
+            out[r].append(Action(s, Op.F, m))
+        elif kind == "I":
+            if wrap:
+                ip[r] += 1
+                in_flight_rank[r] -= 1
+            else:
+                next_i[s] += 1
+                in_flight_stage[s] -= 1
+            wq[r].append((s, m))
+            dur = ci
+            out[r].append(Action(s, Op.I, m))
+        else:
+            wq[r].pop(0)
+            dur = cw
+            out[r].append(Action(s, Op.W, m))
+        finish[(s, kind, m)] = t + dur
+        free_at[r] = t + dur
+        left[r] -= 1
+    if return_makespan:
+        return out, max(free_at.values())
+    return out
+
+
+def tuned_zero_bubble_costed(P: int, v: int, n_mb: int, cost: Dict[int, tuple], comm_latency: float = 0.0,
+                             extra_in_flight: tuple = (0, 1, 2), pending_w: Optional[tuple] = None,
+                             placement: Optional[Dict[int, int]] = None, slack: float = 0.003) -> Schedule:
+    """Replays a few settings of the two limits of :func:`zero_bubble_costed` and keeps, among those within
+    ``slack`` of the shortest makespan, the one that holds the fewest microbatches in flight."""
+    pending_w = pending_w or (P, 2 * P, 4 * P)
+    tried = []
+    for extra in extra_in_flight:
+        for mpw in pending_w:
+            try:
+                sched, span = zero_bubble_costed(P, v, n_mb, cost, comm_latency, mpw, extra, placement, True)
+            except RuntimeError:
+                continue  # this pair of limits blocks itself; the others are still candidates
+            tried.append((span, extra, mpw, sched))
+    if not tried:
+        raise RuntimeError("no setting of the zero-bubble limits produced a schedule")
+    best = min(t[0] for t in tried)
+    close = [t for t in tried if t[0] <= best * (1.0 + slack)]
+    return min(close, key=lambda t: (t[1], t[2], t[0]))[3]
+
+
 def with_reduce_grad(schedule: Schedule) -> Schedule:
     """Appends a REDUCE_GRAD action right after the last weight-producing action (B or W) of every stage."""
     out: Schedule = {}

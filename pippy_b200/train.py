@@ -46,6 +46,7 @@ class Pipeline:
     losses: List[torch.Tensor] = field(default_factory=list)
 
     tied: Any = None
+    pre_optimizer: List[Callable[[], None]] = field(default_factory=list)  # run after the schedule, before the update
 
     def train_step(self, inputs=None, target=None) -> Optional[torch.Tensor]:
         """One optimizer step over one global batch. The rank holding the first stage passes ``inputs``, the rank
@@ -58,6 +59,8 @@ class Pipeline:
             self.schedule.step(*args)
         if self.tied is not None:
             self.tied.sync_grads()
+        for hook in self.pre_optimizer:
+            hook()
         if self.optimizer is not None:
             self.optimizer.step(grad_scale=1.0 / self.n_microbatches, zero_grad=True)
         if self.holds_last and self.losses:
@@ -281,3 +284,73 @@ def build_mixtral_pipeline(
     sched = cls(stages[0], n_microbatches, **kw) if schedule in ("gpipe", "1f1b") else cls(stages, n_microbatches, **kw)
     return Pipeline(stages, sched, opt, flat_dense, n_microbatches, holds_first=(pp_rank == 0),
                     holds_last=((num_stages - 1) % pp_size == pp_rank))
+
+
+def build_llama_tp_pipeline(
+    cfg: LlamaConfig,
+    global_batch: int,
+    seq_len: int,
+    n_microbatches: int,
+    device: torch.device,
+    schedule: str = "1f1b",
+    pp_group: Optional[dist.ProcessGroup] = None,
+    tp_group: Optional[dist.ProcessGroup] = None,
+    dtype: torch.dtype = torch.bfloat16,
+    lr: float = 3e-4,
+    weight_decay: float = 0.1,
+    seed: int = 0,
+    record_timing: bool = False,
+) -> Pipeline:
+    """Llama stages under tensor (+ sequence) x pipeline parallelism, one stage per pipeline rank.  Every
+    tensor-parallel rank of the first stage receives the same token ids and every one of the last stage the same
+    labels; between stages each rank ships its own token shard ``[mb * seq / tp, dim]`` to the same tensor-parallel
+    rank of the next stage."""
+    from .models.llama_tp import build_tp_llama_stage
+    from .parallel.tp import TPContext
+
+    if schedule not in ("gpipe", "1f1b"):
+        raise ValueError("the tensor-parallel builder runs one stage per pipeline rank (gpipe or 1f1b)")
+    pp_rank, pp_size = dist.get_rank(pp_group), dist.get_world_size(pp_group)
+    tp_rank, tp_size = dist.get_rank(tp_group), dist.get_world_size(tp_group)
+    mb = global_batch // n_microbatches
+    rows = mb * seq_len // tp_size
+    tp = TPContext(tp_group, max_rows=rows, max_cols=max(cfg.dim, 2 * cfg.ffn_dim // tp_size), device=device)
+    torch.manual_seed(seed + pp_rank * 100 + tp_rank)
+    module = build_tp_llama_stage(cfg, pp_rank, pp_size, tp, tp_size, tp_rank, mb, seq_len, device=device, dtype=dtype)
+    first, last = pp_rank == 0, pp_rank == pp_size - 1
+    inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if first
+           else torch.empty(rows, cfg.dim, dtype=dtype, device="meta"))
+    out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if last
+           else torch.empty(rows, cfg.dim, dtype=dtype, device="meta"))
+    stage = ManualPipelineStage(module, pp_rank, pp_size, device, n_microbatches, input_args=inp, output_args=out,
+                                group=pp_group)
+    # Sharded weights have local gradients.  The LM head is replicated and sees all tokens on every rank, so its
+    # gradient already agrees.  Norm weights and the embedding are replicated but work on this rank's token shard:
+    # their gradients are partial sums and are added up over the tensor-parallel group (fused NVLink all-reduce).
+    seq_parallel = [p_ for n, p_ in module.named_parameters()
+                    if n.endswith("norm.weight") or n.startswith("tok_embeddings.")]
+    ids_sp = {id(p_) for p_ in seq_parallel}
+    rest = [p_ for p_ in module.parameters() if id(p_) not in ids_sp]
+    if tp_size > 1:
+        # replicated parameters start from tensor-parallel rank 0's values (the shards are seeded per rank)
+        src = dist.get_global_rank(tp_group, 0) if tp_group is not None else 0
+        for n, p_ in module.named_parameters():
+            if id(p_) in ids_sp or n.startswith("output."):
+                dist.broadcast(p_.data, src=src, group=tp_group)
+    flat_sp, flat = FlatParams(seq_parallel), FlatParams(rest)
+    opt = FusedAdamW([flat, flat_sp], lr=lr, weight_decay=weight_decay)
+    hooks = []
+    if tp_size > 1:
+        from .parallel.dp import GradReducer
+
+        reducer = GradReducer(flat_sp, tp_group, average=False)
+
+        def _sum_sequence_parallel_grads():
+            reducer.reduce_all()
+            reducer.finish()
+
+        hooks.append(_sum_sequence_parallel_grads)
+    sched = SCHEDULES[schedule](stage, n_microbatches, loss_fn=causal_lm_loss, record_timing=record_timing,
+                                return_outputs=False)
+    return Pipeline([stage], sched, opt, flat, n_microbatches, holds_first=first, holds_last=last,
+                    pre_optimizer=hooks)
