@@ -49,6 +49,11 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (quick checks only)")
     ap.add_argument("--virtual", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-retune", action="store_true",
+                    help="keep the zero-bubble order of the fixed 2:3:2 cost guess instead of rebuilding it from the "
+                         "per-stage times measured in the second warm-up step")
+    ap.add_argument("--comm-latency-ms", type=float, default=1.0,
+                    help="assumed time for an activation to reach the next rank, used by the cost-aware order")
     ap.add_argument("--sm-reserve", type=int, default=None,
                     help="SMs kept out of the GEMM grid for communication kernels (default: 0 on 1 GPU, 8 otherwise)")
     args = ap.parse_args()
@@ -283,9 +288,19 @@ def main() -> None:
         return float(t.item())
 
     # ---------------------------------------------------------------- warm-up
+    # The second warm-up step of a zero-bubble run is timed per action, and the order of the remaining steps is
+    # rebuilt from those measured per-stage costs (the generator's default is a 2:3:2 guess with equal stages).
     loss = None
+    retuned = None
     for i in range(args.warmup):
+        measure = (i == 1 and world > 1 and hasattr(pipe.schedule, "retune_from_last_step")
+                   and not args.no_retune and args.warmup >= 3)
+        if measure:
+            pipe.schedule.record_timing = True
         loss = pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
+        if measure:
+            pipe.schedule.record_timing = False
+            retuned = pipe.schedule.retune_from_last_step(comm_latency=args.comm_latency_ms * 1e-3)
     barrier()
     _lib.check_device_errors()
 
@@ -412,6 +427,7 @@ def main() -> None:
                 "parallelism": info["parallelism"],
                 "schedule": schedule,
                 "sm_reserve": sm_reserve,
+                "order": ("measured per-stage costs" if retuned is not None else "generator defaults"),
                 "optimizer": "AdamW lr 3e-4 (fused, fp32 moments, fp32 gradient accumulation)",
                 "l2": "inputs larger than L2 (13.5 GB of weights and GBs of activations stream every step)",
             },

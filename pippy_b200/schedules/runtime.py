@@ -105,9 +105,13 @@ class _Timer:
             starts = [s - self.t_begin for _, s, _ in self.records]
         busy = sum(d for _, d in durs)
         per_op: Dict[str, float] = defaultdict(float)
+        per_stage: Dict[Tuple[int, str], List[float]] = defaultdict(list)
         for a, d in durs:
             per_op[a.op.value] += d
+            per_stage[(a.stage, a.op.value)].append(d)
         return {
+            # mean duration of one microbatch's F / B / I / W on each local stage: what a cost-aware schedule needs
+            "per_stage_op_mean_s": {f"{s}:{o}": sum(v) / len(v) for (s, o), v in per_stage.items()},
             "wall_s": wall,
             "busy_s": busy,
             "bubble": (1.0 - busy / wall) if wall > 0 else 0.0,
@@ -503,6 +507,8 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
         super().__init__(stages, n_microbatches, loss_fn, output_merge_spec, **kw)
         self.max_pending_w = max_pending_w
         self.extra_in_flight = extra_in_flight
+        self.stage_costs: Optional[Dict[int, Tuple[float, float, float]]] = None
+        self.comm_latency = 0.0
         if self._num_local > 1 and n_microbatches % self.pp_group_size != 0:
             raise ValueError(
                 f"interleaved zero-bubble requires the number of microbatches ({n_microbatches}) to be a multiple of "
@@ -512,9 +518,46 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
     def _compute_order(self) -> Schedule:
         if not self._has_backward:
             return generators.interleaved_1f1b(self.pp_group_size, self._num_local, self._n_microbatches, False)
+        if self.stage_costs is not None:
+            return generators.tuned_zero_bubble_costed(
+                self.pp_group_size, self._num_local, self._n_microbatches, self.stage_costs, self.comm_latency
+            )
         return generators.zero_bubble(
             self.pp_group_size, self._num_local, self._n_microbatches, self.max_pending_w, self.extra_in_flight
         )
+
+    def set_stage_costs(self, costs: Dict[int, Tuple[float, float, float]], comm_latency: float = 0.0) -> None:
+        """Rebuilds the order from measured costs: ``costs[s] = (forward, input-gradient, weight-gradient)`` seconds
+        per microbatch for EVERY stage of the pipeline, identical on every rank (the order is derived from them
+        deterministically, and all ranks must derive the same one)."""
+        if sorted(costs) != list(range(self.num_stages)):
+            raise ValueError(f"costs must cover stages 0..{self.num_stages - 1}")
+        self.stage_costs = {int(s): tuple(float(x) for x in c) for s, c in costs.items()}
+        self.comm_latency = float(comm_latency)
+        self._build()
+
+    def retune_from_last_step(self, comm_latency: float = 0.0) -> Dict[int, Tuple[float, float, float]]:
+        """Collective over the pipeline group: gathers every rank's measured per-stage F / I / W means of the last
+        step (which must have run with ``record_timing``) and rebuilds the order from them."""
+        if self.last_step_stats is None:
+            raise RuntimeError("run one step with record_timing=True first")
+        mine = self.last_step_stats["per_stage_op_mean_s"]
+        tables: List[Optional[dict]] = [None] * self.pp_group_size
+        if self.pp_group_size > 1:
+            dist.all_gather_object(tables, mine, group=self._stages[0].group)
+        else:
+            tables = [mine]
+        merged: Dict[str, float] = {}
+        for t in tables:
+            merged.update(t)
+        costs = {}
+        for s in range(self.num_stages):
+            f, i, w = merged.get(f"{s}:F"), merged.get(f"{s}:I"), merged.get(f"{s}:W")
+            if f is None or i is None or w is None:
+                raise RuntimeError(f"no measured F / I / W time for stage {s}: the last step did not run a split backward")
+            costs[s] = (f, i, w)
+        self.set_stage_costs(costs, comm_latency)
+        return costs
 
 
 ScheduleZeroBubble = ScheduleInterleavedZeroBubble

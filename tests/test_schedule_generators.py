@@ -175,3 +175,50 @@ def test_placement_errors():
         G.zero_bubble_placed(2, {0: 0, 1: 1, 3: 0}, 4)
     with pytest.raises(ValueError):
         G.zero_bubble_placed(2, {0: 0, 1: 0, 2: 0, 3: 0}, 4)
+
+
+@pytest.mark.parametrize("P,v", [(2, 2), (4, 2), (8, 2), (4, 1)])
+def test_costed_zero_bubble_is_valid_and_no_slower_than_the_fixed_guess(P, v):
+    """The order built from per-stage costs (a heavy last stage, I : W unlike 3 : 2, a transfer latency) runs every
+    action once, respects the dependencies, and replayed on those same costs is not slower than the default order."""
+    from pippy_b200.schedules import generators as g
+    from pippy_b200.schedules.actions import Op, validate
+
+    n, S = 16, P * v
+    cost = {s: (6.0, 9.5, 5.0) for s in range(S)}
+    cost[S - 1] = (8.0, 11.0, 7.0)
+    lat = 0.3
+
+    def replay(sched):
+        finish, clock, ptr = {}, {r: 0.0 for r in sched}, {r: 0 for r in sched}
+        moved = True
+        while moved:
+            moved = False
+            for r in sched:
+                while ptr[r] < len(sched[r]):
+                    a = sched[r][ptr[r]]
+                    s, m = a.stage, a.mb
+                    if a.op == Op.F:
+                        deps = [(s - 1, "F", m)] if s > 0 else []
+                    elif a.op == Op.I:
+                        deps = [(s, "F", m)] + ([(s + 1, "I", m)] if s < S - 1 else [])
+                    else:
+                        deps = [(s, "I", m)]
+                    if any(d not in finish for d in deps):
+                        break
+                    start = max([clock[r]] + [finish[d] + (lat if d[0] % P != r else 0.0) for d in deps])
+                    end = start + cost[s]["FIW".index(a.op.value)]
+                    finish[(s, a.op.value, m)] = clock[r] = end
+                    ptr[r] += 1
+                    moved = True
+        assert all(ptr[r] == len(sched[r]) for r in sched)
+        return max(clock.values())
+
+    fixed = g.zero_bubble(P, v, n)
+    costed = g.tuned_zero_bubble_costed(P, v, n, cost, lat)
+    validate(costed, S, n, lambda s: s % P)
+    assert replay(costed) <= replay(fixed) * 1.001
+    # the V-shaped placement goes through the same generator
+    if v == 2:
+        placed = g.zero_bubble_costed(P, 2, n, cost, lat, placement=g.v_placement(P))
+        validate(placed, S, n, lambda s: g.v_placement(P)[s])
