@@ -367,6 +367,16 @@ def main() -> None:
     per_op = {k: max_over_ranks(stats["per_op_s"].get(k, 0.0)) for k in ("F", "B", "I", "W")}
     busy_min = -max_over_ranks(-stats["busy_s"])
     busy_max = max_over_ranks(stats["busy_s"])
+    # every stage's mean F / B / I / W milliseconds per microbatch and every rank's busy time, for the record
+    stage_ms, busy_per_rank = dict(stats["per_stage_op_mean_s"]), [stats["busy_s"]]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (stage_ms, stats["busy_s"]))
+        stage_ms, busy_per_rank = {}, []
+        for tbl, b in gathered:
+            stage_ms.update(tbl)
+            busy_per_rank.append(b)
+    stage_ms = {k: round(v * 1e3, 3) for k, v in sorted(stage_ms.items(), key=lambda kv: (int(kv[0].split(":")[0]), kv[0]))}
     dump_dir = os.environ.get("PIPPY_TIMELINE_DIR")
     if dump_dir:
         os.makedirs(dump_dir, exist_ok=True)
@@ -441,6 +451,8 @@ def main() -> None:
         out["bubble_measured"] = bubble
         out["per_op_s_max_rank"] = per_op
         out["busy_s_min_max_rank"] = [busy_min, busy_max]
+        out["busy_s_per_rank"] = [round(b, 4) for b in busy_per_rank]
+        out["stage_op_ms"] = stage_ms
         if like_for_like is not None:
             out["interleaved_1f1b"] = like_for_like
         print(json.dumps(out), flush=True)

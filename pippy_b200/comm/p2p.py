@@ -42,11 +42,17 @@ def new_groups_worldwide(requests: List[List[int]], pg_options_factory=None) -> 
 class LinkGroups:
     """``groups[(src_group_rank, dst_group_rank, kind)]`` -> ProcessGroup, kind in {"F", "B"}."""
 
-    def __init__(self, pp_group: Optional[dist.ProcessGroup], links: Iterable[Tuple[int, int]], max_ctas: int = 2):
-        """``max_ctas`` caps the thread blocks of each link's NCCL kernels.  A point-to-point kernel spins on its
+    def __init__(self, pp_group: Optional[dist.ProcessGroup], links: Iterable[Tuple[int, int]],
+                 max_ctas: Optional[int] = None):
+        """``max_ctas`` (default 2, or the environment variable ``PIPPY_P2P_MAX_CTAS``) caps the thread blocks of
+        each link's NCCL kernels.  A point-to-point kernel spins on its
         SMs until the peer arrives; with the default channel count it would take dozens of SMs away from the
         persistent compute kernels for that long.  Two blocks move a 64 MiB activation in about a millisecond,
         which hides behind tens of milliseconds of stage compute."""
+        import os
+
+        if max_ctas is None:
+            max_ctas = int(os.environ.get("PIPPY_P2P_MAX_CTAS", "2"))
         self.pp_group = pp_group
         self.groups: Dict[Tuple[int, int, str], dist.ProcessGroup] = {}
         if not dist.is_initialized():

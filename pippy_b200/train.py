@@ -86,7 +86,7 @@ def build_llama_pipeline(
     seed: int = 0,
     record_timing: bool = False,
     schedule_kwargs: Optional[dict] = None,
-    balance: bool = True,
+    balance: Any = True,
     dp_group: Optional[dist.ProcessGroup] = None,
     activation_checkpointing: bool = False,
 ) -> Pipeline:
@@ -121,6 +121,12 @@ def build_llama_pipeline(
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
         out = (torch.empty(mb, seq_len, cfg.vocab_size, dtype=dtype, device="meta") if s == num_stages - 1
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
+        # a stage that starts or ends inside a layer's attention or MLP half also takes / hands over that half's
+        # intermediate (the attention output or the SwiGLU output)
+        if module.carry_in:
+            inp = (inp, torch.empty(mb, seq_len, module.carry_in, dtype=dtype, device="meta"))
+        if module.carry_out:
+            out = (out, torch.empty(mb, seq_len, module.carry_out, dtype=dtype, device="meta"))
         stages.append(ManualPipelineStage(module, s, num_stages, device, n_microbatches, input_args=inp,
                                           output_args=out, group=group))
         params.extend(module.parameters())
