@@ -320,7 +320,13 @@ def build_llama_tp_pipeline(
     tp_rank, tp_size = dist.get_rank(tp_group), dist.get_world_size(tp_group)
     mb = global_batch // n_microbatches
     rows = mb * seq_len // tp_size
-    tp = TPContext(tp_group, max_rows=rows, max_cols=max(cfg.dim, 2 * cfg.ffn_dim // tp_size), device=device)
+    if device.type == "cuda":
+        tp = TPContext(tp_group, max_rows=rows, max_cols=max(cfg.dim, 2 * cfg.ffn_dim // tp_size), device=device)
+    else:
+        # CPU (tests): the layers fall back to plain all-gather / reduce-scatter statements and only need the group
+        from types import SimpleNamespace
+
+        tp = SimpleNamespace(group=tp_group, world=tp_size, rank=tp_rank)
     torch.manual_seed(seed + pp_rank * 100 + tp_rank)
     module = build_tp_llama_stage(cfg, pp_rank, pp_size, tp, tp_size, tp_rank, mb, seq_len, device=device, dtype=dtype)
     first, last = pp_rank == 0, pp_rank == pp_size - 1

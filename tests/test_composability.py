@@ -266,3 +266,87 @@ def _gpt2_v_shape(rank, world):
 
 def test_gpt2_v_shaped_schedule_keeps_tied_weights_on_one_rank():
     run_ranks(_gpt2_v_shape, 2, timeout_s=240)
+
+
+def _llama_tp_pp(rank, world):
+    """Tensor (+ sequence) parallel x pipeline on a 2 x 2 gloo mesh against the same weights gathered into one
+    unsharded model: loss, and the gradients of replicated parameters that work on token shards (norm weights,
+    embedding: partial sums added over the tensor-parallel group) and of sharded ones (local slices)."""
+    import torch.distributed as dist
+
+    from pippy_b200.models.llama import Llama, LlamaConfig, causal_lm_loss
+    from pippy_b200.parallel.mesh import init_mesh
+    from pippy_b200.train import build_llama_tp_pipeline
+
+    mesh = init_mesh(pp_size=2, tp_size=2)
+    cfg = LlamaConfig(vocab_size=96, dim=32, n_layers=2, n_heads=4, ffn_dim=64)
+    B, S, n_mb = 4, 8, 2
+    pipe = build_llama_tp_pipeline(cfg, B, S, n_mb, torch.device("cpu"), schedule="1f1b", pp_group=mesh.pp_group,
+                                   tp_group=mesh.tp_group, dtype=torch.float32, lr=0.0, weight_decay=0.0)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(21))
+    losses = []
+    if pipe.holds_first and pipe.holds_last:
+        pipe.schedule.step(ids, target=ids, losses=losses)
+    elif pipe.holds_first:
+        pipe.schedule.step(ids)
+    elif pipe.holds_last:
+        pipe.schedule.step(target=ids, losses=losses)
+    else:
+        pipe.schedule.step()
+    for hook in pipe.pre_optimizer:
+        hook()
+    for grp in pipe.optimizer.groups:
+        grp.fold_autograd_grads()
+
+    # gather every rank's parameters and gradients and rebuild the unsharded model on every rank
+    mine = {f"{mesh.pp_rank}:{mesh.tp_rank}:{n}": (p.detach().clone(), p.main_grad.clone())
+            for n, p in pipe.stages[0].submod.named_parameters()}
+    everything = [None] * world
+    dist.all_gather_object(everything, mine)
+    table = {k: v for part in everything for k, v in part.items()}
+    hd, H = cfg.head_dim, cfg.n_heads // 2
+    full = Llama(cfg, dtype=torch.float32)
+
+    def join(pp, name, which):
+        a, b = table[f"{pp}:0:{name}"][which], table[f"{pp}:1:{name}"][which]
+        if name.endswith("wqkv.weight"):  # each shard is [q heads | k heads | v heads] of its rank
+            qa, ka, va = a.split(H * hd)
+            qb, kb, vb = b.split(H * hd)
+            return torch.cat([qa, qb, ka, kb, va, vb])
+        if name.endswith("w_gate_up.weight"):  # each shard is [gate | up] of its rank
+            ga, ua = a.chunk(2)
+            gb, ub = b.chunk(2)
+            return torch.cat([ga, gb, ua, ub])
+        if name.endswith("wo.weight") or name.endswith("w_down.weight"):
+            return torch.cat([a, b], dim=1)
+        return a  # replicated
+
+    names = {}
+    for k in table:
+        pp, tpr, name = k.split(":", 2)
+        names[name] = int(pp)
+    with torch.no_grad():
+        for name, p in full.named_parameters():
+            key = name.replace("attention.wqkv", "wqkv").replace("attention.wo", "wo") \
+                      .replace("feed_forward.w_gate_up", "w_gate_up").replace("feed_forward.w_down", "w_down")
+            p.copy_(join(names[key], key, 0))
+    total = 0.0
+    for mb_ids in ids.chunk(n_mb):
+        l = causal_lm_loss(full(mb_ids), mb_ids)
+        l.backward()
+        total += float(l)
+    if losses:
+        assert abs(float(torch.stack(losses).sum()) - total) < 1e-4
+    for name, p in full.named_parameters():
+        key = name.replace("attention.wqkv", "wqkv").replace("attention.wo", "wo") \
+                  .replace("feed_forward.w_gate_up", "w_gate_up").replace("feed_forward.w_down", "w_down")
+        torch.testing.assert_close(join(names[key], key, 1), p.grad, rtol=1e-4, atol=1e-5, msg=name)
+        if not any(key.endswith(t) for t in ("wqkv.weight", "w_gate_up.weight", "wo.weight", "w_down.weight")):
+            # replicated parameters carry the same gradient on both tensor-parallel ranks
+            torch.testing.assert_close(table[f"{names[key]}:0:{key}"][1], table[f"{names[key]}:1:{key}"][1],
+                                       rtol=1e-5, atol=1e-6, msg=name)
+    dist.barrier()
+
+
+def test_llama_tp2_pp2_matches_unsharded_model():
+    run_ranks(_llama_tp_pp, 4, timeout_s=240)
