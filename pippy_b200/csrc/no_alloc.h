@@ -14,8 +14,13 @@
 // the process exits.  H above pb_rmsnorm_bwd_noalloc_max_hidden() (8192) is rejected with -2; nothing is
 // truncated.  The call makes no cudaMalloc/cudaFree and calls no allocating library routine.
 //
+// Work split: the rows are spread over at most 128 CTAs (the number of partial rows the array holds), whatever T is;
+// the regular entry point uses two CTAs per SM.  dx is the same bit for bit, dw differs from the regular entry
+// point's by the order in which the per-CTA partial sums are added (fp32 rounding only).
+//
 // First call on each device: the entry point resolves the array's device address (cudaGetSymbolAddress) with that
-// device current, and caches it.  Make that first call outside any stream capture.
+// device current, and caches it (under a mutex, so concurrent first calls from several host threads are safe).
+// Make that first call outside any stream capture.
 //
 // Sharing: all calls on a device use the same array and it keeps the previous call's contents.  Every partial row is
 // fully rewritten before it is read, so nothing has to be cleared, but two calls that overlap on the GPU (different

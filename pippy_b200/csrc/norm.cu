@@ -5,6 +5,7 @@
 // gradient in registers and writes one partial row per CTA to a scratch buffer [grid, H] which a
 // second kernel folds.  dx is produced in the same pass.
 #include <cuda_bf16.h>
+#include <mutex>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -288,6 +289,7 @@ constexpr int NOALLOC_MAX_CTAS = 128;
 static __device__ __align__(256) float g_noalloc_scratch[(size_t)NOALLOC_MAX_CTAS * 2 * NOALLOC_MAX_H];
 constexpr int NOALLOC_MAX_DEVICES = 64;
 static float* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+static std::mutex g_noalloc_setup_mu;  // two host threads may make a device's first call at the same time
 }  // namespace pbn
 
 extern "C" {
@@ -301,14 +303,18 @@ int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const f
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -3;
-  if (g_noalloc_scratch_ptr[dev] == nullptr) {
-    // first call on this device: resolve the device address of the array (its name is only a host-side handle)
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (e != cudaSuccess) return (int)e;
-    g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_setup_mu);
+    if (g_noalloc_scratch_ptr[dev] == nullptr) {
+      // first call on this device: resolve the device address of the array (its name is only a host-side handle)
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_scratch_ptr[dev];
   }
-  float* scratch = g_noalloc_scratch_ptr[dev];
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   int grid = NOALLOC_MAX_CTAS;
   if (grid > T) grid = T;

@@ -9,7 +9,14 @@ mixed-integer program solved with ``scipy.optimize.milp``:
               stage(u) <= stage(v)            for every edge u -> v      (stage(n) = sum_k k * x[n, k])
               sum_n w_n x[n, k] <= MAX_MEMORY_IMBALANCE * total / K      (balanced state)
               sum_n x[n, k] >= 1                                         (no empty stage)
+              cross_k <= MAX_COMMUNICATION_IMBALANCE * mean_j cross_j    (balanced transfers; see below)
   minimise    sum_edges a_e * (stage(v) - stage(u))                     (activation bytes x hops)
+
+``cross_k`` is what crosses the boundary between stages k and k+1: with y[n, k] = sum_{j<=k} x[n, j] ("n runs in
+stage k or earlier") an edge u -> v crosses it exactly when y[u, k] - y[v, k] = 1, so cross_k is linear in x and the
+bound on the busiest boundary relative to the mean is a linear constraint too (the reference bounds its per-stage
+edge weight the same way, pippy/graphsplit.py:48, 270-285).  Some graphs cannot meet it (an embedding output next
+to a wide hidden state); then the program is solved again without it and a warning says so.
 
 The graph is then reordered stage by stage (legal because edges never point to an earlier stage) and a
 ``pipe_split`` marker is placed at every boundary.
@@ -122,9 +129,31 @@ def split_by_graph_with_num_stages(gm: fx.GraphModule, num_stages: int) -> fx.Gr
         r2 = np.zeros(nvar)
         r2[[var(n, k) for n in range(N)]] = 1
         rows.append(r2); lo.append(1); hi.append(N)
-    # prefer balance among equally cheap cuts: tiny penalty on late stages' weight deviation is unnecessary here
-    res = milp(c, constraints=LinearConstraint(np.array(rows), np.array(lo), np.array(hi)),
-               integrality=np.ones(nvar), bounds=Bounds(0, 1), options={"time_limit": SCIPY_TIME_LIMIT_SEC})
+    # balanced transfers: (K - 1) * cross_k - MAX_COMMUNICATION_IMBALANCE * sum_j cross_j <= 0 for every boundary k
+    comm_rows = []
+    if K > 2 and edges:
+        cross = np.zeros((K - 1, nvar))
+        for (u, v), a in edges.items():
+            for k in range(K - 1):
+                for j in range(k + 1):
+                    cross[k, var(u, j)] += a
+                    cross[k, var(v, j)] -= a
+        total_cross = cross.sum(axis=0)
+        for k in range(K - 1):
+            comm_rows.append((K - 1) * cross[k] - MAX_COMMUNICATION_IMBALANCE * total_cross)
+
+    def solve(with_comm: bool):
+        a_rows = rows + (comm_rows if with_comm else [])
+        a_lo = lo + ([-np.inf] * len(comm_rows) if with_comm else [])
+        a_hi = hi + ([0.0] * len(comm_rows) if with_comm else [])
+        return milp(c, constraints=LinearConstraint(np.array(a_rows), np.array(a_lo), np.array(a_hi)),
+                    integrality=np.ones(nvar), bounds=Bounds(0, 1), options={"time_limit": SCIPY_TIME_LIMIT_SEC})
+
+    res = solve(bool(comm_rows))
+    if comm_rows and (res.status != 0 or res.x is None):
+        logger.warning("split_by_graph: no assignment keeps every boundary within %.2fx of the mean transfer; "
+                       "solving without the communication-balance constraint", MAX_COMMUNICATION_IMBALANCE)
+        res = solve(False)
     if res.status == 1:
         raise ValueError(f"graph split did not finish within {SCIPY_TIME_LIMIT_SEC}s; use a size-based policy instead")
     if not res.success or res.x is None:

@@ -37,6 +37,14 @@ def test_example_runs(path, nproc, tmp_path):
     _run(path, nproc)
 
 
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_llama_greedy_decoding_same_tokens_as_unsplit_model(nproc):
+    """Hugging Face Llama through the traced pipeline, greedy decoding of several tokens: the same tokens on 2 and
+    4 ranks as the unsplit model chooses (reference examples/llama/README.md:1-17 expects the same words on 2, 4, 8)."""
+    out = _run("llama/pippy_llama.py", nproc, "--check", "--new-tokens", "3", "--cuda", "0")
+    assert "chose the same 3 token(s)" in out
+
+
 def test_parallel_branches_keep_stage_order():
     """Stages that read the same producer side by side: stage i must be submod_i in the program text and in
     the runtime's topology (fx.split_module emits such branches in an order of its own)."""
