@@ -25,9 +25,12 @@ class _GatherForHead(torch.autograd.Function):
     all tokens, so the backward simply keeps this rank's rows."""
 
     @staticmethod
-    def forward(ctx, x_shard, group):
+    def forward(ctx, x_shard, tp):
+        group = tp.group
         ctx.rows = x_shard.shape[0]
         ctx.rank = dist.get_rank(group)
+        if hasattr(tp, "all_gather_rows") and x_shard.is_cuda:
+            return tp.all_gather_rows(x_shard)  # the package's peer-memory all-gather kernel
         out = torch.empty(dist.get_world_size(group) * x_shard.shape[0], x_shard.shape[1], dtype=x_shard.dtype,
                           device=x_shard.device)
         dist.all_gather_into_tensor(out, x_shard.contiguous(), group=group)
@@ -93,7 +96,7 @@ class TPLlamaStage(nn.Module):
         if self.last:
             h = self.norm(h)
             if self.tp_size > 1:
-                h = _GatherForHead.apply(h, self.tp.group)
+                h = _GatherForHead.apply(h, self.tp)
             return self.output(h).view(B, S, -1)
         return h
 

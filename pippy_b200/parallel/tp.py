@@ -9,7 +9,8 @@ example composes with DTensor (examples/tp+pp/pippy_tp.py:79-112), i.e. NCCL all
 cuBLAS GEMMs.
 
 Backward duals: d(input) of a column-parallel linear is a GEMM -> reduce-scatter, d(input) of a row-parallel linear an
-all-gather -> GEMM; weight gradients are local GEMMs on gathered activations.
+all-gather -> GEMM (whose gathered rows also feed that layer's weight gradient); the column-parallel weight gradient
+re-gathers its input with the package's own peer-memory all-gather kernel and runs a local GEMM.
 """
 from __future__ import annotations
 
@@ -51,8 +52,11 @@ class TPContext:
         self.rs_scratch = torch.empty(max_rows * max_cols, dtype=torch.bfloat16, device=self.device)
         self.tile_flags = torch.zeros(W * max_rows // 256 + 8, dtype=torch.int32, device=self.device)
         self.counters = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self.gather_flags = SymmetricBuffer(4096, group, self.device)
+        self.gather_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.ag_epoch = 0
         self.rs_epoch = 0
+        self.gather_epoch = 0
 
     def _flag_array(self, buf: SymmetricBuffer):
         arr = (ctypes.POINTER(ctypes.c_int) * self.world)()
@@ -107,9 +111,26 @@ class TPContext:
         _lib.check(rc, "pb_gemm_tp_fused(GEMM -> reduce-scatter)")
         return out
 
-    def all_gather_rows(self, x_shard: torch.Tensor) -> torch.Tensor:
-        out = torch.empty(self.world * x_shard.shape[0], x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
-        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
+    def all_gather_rows(self, x_shard: torch.Tensor, ctas: int = 32) -> torch.Tensor:
+        """Concatenation of every rank's ``[rows, cols]`` shard, by this package's peer-memory all-gather kernel
+        (``csrc/peer.cu``: plain vector loads over NVLink, flag handshakes); the shard travels through the same
+        peer-mapped buffer the fused all-gather -> GEMM publishes its input in."""
+        rows, cols = x_shard.shape
+        nbytes = rows * cols * x_shard.element_size()
+        if x_shard.dtype != torch.bfloat16 or nbytes % 16 != 0 or rows > self.max_rows or cols > self.max_cols:
+            out = torch.empty(self.world * rows, cols, dtype=x_shard.dtype, device=x_shard.device)
+            dist.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
+            return out
+        src = self.ag_src.tensor(torch.bfloat16, rows * cols).view(rows, cols)
+        src.copy_(x_shard)
+        out = torch.empty(self.world * rows, cols, dtype=torch.bfloat16, device=x_shard.device)
+        self.gather_epoch += 1
+        rc = _lib.lib().pb_peer_allgather(
+            _lib.ptr(out), self.ag_src.pointer_array(), self._flag_array(self.gather_flags),
+            _lib.ptr(self.gather_counter), _lib.ptr(_lib.err_word(x_shard.device)), _lib.c_ll(nbytes),
+            _lib.c_int(self.rank), _lib.c_int(self.world), _lib.c_int(self.gather_epoch), _lib.c_int(ctas),
+            _lib.stream_ptr())
+        _lib.check(rc, "pb_peer_allgather")
         return out
 
 

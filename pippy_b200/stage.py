@@ -271,10 +271,16 @@ class PipelineStageBase:
                 continue
             is_float = spec.meta is not None and spec.meta.dtype.is_floating_point
             if grad is None and is_float:
-                raise RuntimeError(
-                    f"[{self.stage_index}] input {spec.name!r} comes from stage {spec.source} but has no gradient "
-                    "to send back"
-                )
+                # A floating-point input that nothing differentiable depends on (an attention mask turned into
+                # additive form on an earlier stage, a dropped branch): the producer has posted a receive for its
+                # gradient all the same, since the two sides cannot know this before running, so zeros are sent.
+                # The reference refuses such a boundary (pippy/_PipelineStage.py:336-340).
+                if not hasattr(self, "_zero_grads"):
+                    self._zero_grads: Dict[int, torch.Tensor] = {}
+                grad = self._zero_grads.get(idx)
+                if grad is None:
+                    grad = torch.zeros(spec.meta.shape, dtype=spec.meta.dtype, device=self.device)
+                    self._zero_grads[idx] = grad
             if grad is None:
                 continue
             src_rank = self.rank_of_stage(spec.source)

@@ -64,11 +64,13 @@ def test_gpt2_example_runs_on_two_ranks():
     assert "pipeline output equals the unsplit model" in res.stdout
 
 
-@pytest.mark.parametrize("name", ["gpt2", "bert", "mbart", "llama"])
+@pytest.mark.parametrize("name", sorted(hf_utils.FAMILIES))
 def test_family_trains_through_traced_stages(name):
-    """Forward + backward under 1F1B on two gloo ranks: loss and every parameter gradient equal the unsplit model's;
-    weights tied across stages are replicated and their gradients sum (GPT-2, BERT), encoder outputs skip over the
-    stage boundary into every decoder layer (mBART)."""
+    """Every registered family (reference test/hf_test.py:796-1101 parametrises forward + backward over the model
+    zoo the same way): forward + backward under 1F1B on two gloo ranks, loss and every parameter gradient equal the
+    unsplit model's; weights tied across stages are replicated and their gradients sum (GPT-2, BERT), encoder
+    outputs skip over the stage boundary into every decoder layer (mBART, Blenderbot), a float mask that crosses the
+    boundary without a gradient gets zeros sent back (DeBERTa)."""
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
            "--nproc-per-node", "2", os.path.join(ROOT, "examples", "huggingface", "pippy_hf.py"), "--model", name,
