@@ -126,6 +126,18 @@ long long pb_peer_wait_cycles() { return g_peer_wait_cycles; }
 // `ms` milliseconds at a nominal 2 GHz SM clock; a lower clock only makes the wait longer.  ms <= 0 restores the default.
 void pb_set_peer_wait_ms(double ms) { g_peer_wait_cycles = ms > 0 ? (long long)(ms * 2.0e6) : 6000000000LL; }
 
+// Debug build (-DPB_BOUNDS_CHECK): the error word that out-of-range indices are reported to (see dbgcheck.cuh).
+static int* g_debug_err = nullptr;
+int* pb_debug_err_ptr() { return g_debug_err; }
+void pb_set_debug_err_ptr(int* dev_ptr) { g_debug_err = dev_ptr; }
+int pb_bounds_check_enabled() {
+#ifdef PB_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 int pb_device_sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;

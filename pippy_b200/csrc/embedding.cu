@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "dbgcheck.cuh"
+
 extern "C" void pb_count_launch(int n);
 
 namespace pbm {
@@ -10,7 +12,7 @@ namespace pbm {
 // out[t, :] = wte[ids[t], :] (+ wpe[t % S, :]);  H % 8 == 0
 __global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ wte,
                                  const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out, long long T,
-                                 int H, int S) {
+                                 int H, int S PB_DBG_PARAMS) {
   const int vec = H / 8;
   const long long total = T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -18,6 +20,7 @@ __global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_b
     const long long t = i / vec;
     const int v = (int)(i % vec);
     const long long id = ids[t];
+    if (!PB_DBG_IN_RANGE(id)) continue;  // debug build: a token id outside the table is reported, not read
     uint4 a = __ldg(reinterpret_cast<const uint4*>(wte + id * H) + v);
     if (wpe) {
       uint4 p = __ldg(reinterpret_cast<const uint4*>(wpe + (long long)(t % S) * H) + v);
@@ -35,13 +38,15 @@ __global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_b
 
 // dwte[ids[t], :] += dout[t, :]  (fp32 table, vector atomics);  dwpe[t % S, :] += dout[t, :]
 __global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
-                                 float* __restrict__ dwte, float* __restrict__ dwpe, long long T, int H, int S) {
+                                 float* __restrict__ dwte, float* __restrict__ dwpe, long long T, int H, int S
+                                 PB_DBG_PARAMS) {
   const int vec = H / 4;
   const long long total = T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / vec;
     const int v = (int)(i % vec);
+    if (!PB_DBG_IN_RANGE(ids[t])) continue;
     const uint2 raw = *reinterpret_cast<const uint2*>(dout + t * H + v * 4);
     const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
     const float2 lo = __bfloat1622float2(b[0]), hi = __bfloat1622float2(b[1]);
@@ -55,8 +60,9 @@ __global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_b
 
 extern "C" {
 
+// `vocab` (rows of wte) is only used by the debug build's bounds check.
 int pb_embed_fwd(const long long* ids, const void* wte, const void* wpe, void* out, long long T, int H, int S,
-                 void* stream_) {
+                 long long vocab, void* stream_) {
   using namespace pbm;
   if (H % 8 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -64,20 +70,22 @@ int pb_embed_fwd(const long long* ids, const void* wte, const void* wpe, void* o
   if (g > 148 * 16) g = 148 * 16;
   embed_fwd_kernel<<<(unsigned)g, 256, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(wte),
                                                     reinterpret_cast<const __nv_bfloat16*>(wpe),
-                                                    reinterpret_cast<__nv_bfloat16*>(out), T, H, S);
+                                                    reinterpret_cast<__nv_bfloat16*>(out), T, H, S PB_DBG_ARGS(vocab));
+  (void)vocab;
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
 
 int pb_embed_bwd(const long long* ids, const void* dout, float* dwte, float* dwpe, long long T, int H, int S,
-                 void* stream_) {
+                 long long vocab, void* stream_) {
   using namespace pbm;
   if (H % 4 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   long long g = (T * (H / 4) + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
   embed_bwd_kernel<<<(unsigned)g, 256, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(dout), dwte, dwpe, T,
-                                                    H, S);
+                                                    H, S PB_DBG_ARGS(vocab));
+  (void)vocab;
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

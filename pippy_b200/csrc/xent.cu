@@ -6,6 +6,8 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include "dbgcheck.cuh"
+
 extern "C" void pb_count_launch(int n);
 
 namespace pbx {
@@ -35,14 +37,16 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 __global__ void __launch_bounds__(THREADS) xent_fwd_bwd_kernel(const __nv_bfloat16* logits, __nv_bfloat16* dlogits,
                                                                const long long* __restrict__ targets,
                                                                float* __restrict__ loss_rows, int V, long long ld,
-                                                               float grad_scale, long long ignore_index) {
+                                                               float grad_scale, long long ignore_index
+                                                               PB_DBG_PARAMS) {
   __shared__ float red_m[THREADS / 32];
   __shared__ float red_s[THREADS / 32];
   __shared__ float bc[2];
   const long long row = blockIdx.x;
   const __nv_bfloat16* lr = logits + row * ld;
   __nv_bfloat16* dr = dlogits + row * ld;
-  const long long tgt = targets[row];
+  long long tgt = targets[row];
+  if (tgt != ignore_index && !PB_DBG_IN_RANGE(tgt)) tgt = ignore_index;  // debug build: reported, row skipped
   const int nvec = V / 8;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
@@ -137,7 +141,7 @@ int pb_xent_fwd_bwd(const void* logits, void* dlogits, const long long* targets,
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   xent_fwd_bwd_kernel<<<(unsigned)T, THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
                                                            reinterpret_cast<__nv_bfloat16*>(dlogits), targets,
-                                                           loss_rows, V, ld, grad_scale, ignore_index);
+                                                           loss_rows, V, ld, grad_scale, ignore_index PB_DBG_ARGS(V));
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

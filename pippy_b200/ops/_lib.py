@@ -16,7 +16,10 @@ _LIB = None
 _LOCK = threading.Lock()
 _ERR_WORDS: dict[int, torch.Tensor] = {}
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libpippy_b200.so")
+_LIB_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib")
+# PIPPY_BOUNDS_CHECK=1 selects the debug library, whose kernels validate the indices they read from tensors
+LIB_PATH = os.path.join(_LIB_DIR, "libpippy_b200_dbg.so" if os.environ.get("PIPPY_BOUNDS_CHECK", "0") == "1"
+                        else "libpippy_b200.so")
 
 c_void_p = ctypes.c_void_p
 c_int = ctypes.c_int
@@ -66,7 +69,15 @@ def err_word(device: torch.device | None = None) -> torch.Tensor:
     if w is None:
         w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _ERR_WORDS[idx] = w
+        if lib().pb_bounds_check_enabled():
+            # debug build: kernels without an error-word argument of their own report through this one
+            lib().pb_set_debug_err_ptr(c_void_p(w.data_ptr()))
     return w
+
+
+def bounds_check_enabled() -> bool:
+    """True when the library was built with ``PIPPY_BOUNDS_CHECK=1`` (index validation in the kernels)."""
+    return bool(available() and lib().pb_bounds_check_enabled())
 
 
 def check_device_errors() -> None:
@@ -75,7 +86,8 @@ def check_device_errors() -> None:
         code = int(w.item())
         if code != 0:
             w.zero_()
-            raise KernelError(f"device {idx}: kernel error code {code} (1 = bounded wait ran out, 3 = peer wait ran out)")
+            raise KernelError(f"device {idx}: kernel error code {code} (1 = bounded wait ran out, 3 = peer wait ran out, "
+                              "4 = MoE receive buffer overflow, 5 = index out of range in a bounds-checking build)")
 
 
 def check(rc: int, what: str) -> None:

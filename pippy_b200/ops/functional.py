@@ -506,7 +506,7 @@ def _embed_wgrad(ids, dout, wte, wpe, S):
         dp = pmg if (pmg is not None and pmg.dtype == torch.float32) else torch.zeros(wpe.shape, dtype=torch.float32, device=wpe.device)
     _lib.check(
         _lib.lib().pb_embed_bwd(_lib.ptr(ids), _lib.ptr(dout), _lib.ptr(dw), _lib.ptr(dp), _lib.c_ll(T),
-                                _lib.c_int(H), _lib.c_int(S), _lib.stream_ptr()),
+                                _lib.c_int(H), _lib.c_int(S), _lib.c_ll(wte.shape[0]), _lib.stream_ptr()),
         "pb_embed_bwd",
     )
     if dw is not wmg:
@@ -523,7 +523,7 @@ class _EmbeddingFn(torch.autograd.Function):
         out = torch.empty(T, H, device=wte.device, dtype=wte.dtype)
         _lib.check(
             _lib.lib().pb_embed_fwd(_lib.ptr(flat), _lib.ptr(wte), _lib.ptr(wpe), _lib.ptr(out), _lib.c_ll(T),
-                                    _lib.c_int(H), _lib.c_int(S), _lib.stream_ptr()),
+                                    _lib.c_int(H), _lib.c_int(S), _lib.c_ll(wte.shape[0]), _lib.stream_ptr()),
             "pb_embed_fwd",
         )
         ctx.save_for_backward(flat)

@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from ..optim import FlatParams
+from ..utils import streamcheck
 
 
 class GradReducer:
@@ -90,6 +91,11 @@ class GradReducer:
         ready = torch.cuda.Event()
         ready.record(cur)
         self._stream.wait_event(ready)
+        chk = streamcheck.tracker()
+        if chk is not None:  # debug mode: the gradients were produced on `cur`, the reduction rewrites them on the side stream
+            chk.write(f"grad@{id(self.flat)}", cur.cuda_stream)
+            chk.ordered(cur.cuda_stream, self._stream.cuda_stream)
+            chk.write(f"grad@{id(self.flat)}", self._stream.cuda_stream)
         with torch.cuda.stream(self._stream):
             self.epoch += 1
             grid = ctypes.c_int(0)
@@ -113,4 +119,14 @@ class GradReducer:
         cur = torch.cuda.current_stream() if self._stream is not None else None
         for ev in self._pending:
             cur.wait_event(ev)
+        chk = streamcheck.tracker()
+        if chk is not None and self._stream is not None and self._pending:
+            chk.ordered(self._stream.cuda_stream, cur.cuda_stream)
         self._pending.clear()
+
+    def check_read(self) -> None:
+        """Debug mode only: declares that the current stream is about to read (or rescale) the gradients; raises
+        ``StreamOrderError`` if a reduction is still in flight on the side stream (``finish()`` was not called)."""
+        chk = streamcheck.tracker()
+        if chk is not None and self._stream is not None:
+            chk.read(f"grad@{id(self.flat)}", torch.cuda.current_stream().cuda_stream)

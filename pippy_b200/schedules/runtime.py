@@ -377,6 +377,8 @@ class PipelineSchedule:
         # them before anything else (the scaling below, the optimizer) touches the gradients
         if self.grad_reducer is not None and self._has_backward:
             self.grad_reducer.finish()
+        if self.grad_reducer is not None and hasattr(self.grad_reducer, "check_read"):
+            self.grad_reducer.check_read()  # debug mode (PIPPY_STREAM_CHECK=1): fails if a reduction is still in flight
         if self.scale_grads and self._has_backward:
             for st in self._stages:
                 st.scale_grads(self._n_microbatches)

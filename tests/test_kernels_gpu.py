@@ -430,3 +430,47 @@ def test_moe_layer_one_rank_against_dense(T):
         assert _rel(fused.w_down.grad, dense.w_down.grad) < 2e-2, ("dWdown", it)
         assert _rel(fused.w_gate_up.grad, dense.w_gate_up.grad) < 2e-2, ("dWgu", it)
         assert abs(float(fused.last_aux_loss) - float(dense.last_aux_loss)) < 1e-3
+
+
+def test_bounds_checking_library_reports_bad_indices():
+    """The debug library (PIPPY_BOUNDS_CHECK=1) validates indices read from tensors: a token id and a class label
+    outside their tables are reported through the device error word and the accesses are skipped, so the kernels
+    finish, the context stays usable and the in-range rows are still right."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = """
+import torch
+from pippy_b200.ops import _lib, functional as pf
+assert _lib.bounds_check_enabled()
+_lib.err_word(torch.device("cuda", 0))
+wte = torch.randn(100, 64, device="cuda").bfloat16()
+ids = torch.tensor([[1, 5, 250, 7]], device="cuda")          # 250 is outside the 100-row table
+out = pf.embedding(ids, wte)
+torch.cuda.synchronize()
+assert torch.equal(out[0], wte[1]) and torch.equal(out[3], wte[7])
+try:
+    _lib.check_device_errors()
+    raise SystemExit("the bad token id was not reported")
+except _lib.KernelError as e:
+    assert "code 5" in str(e), e
+logits = torch.randn(4, 104, device="cuda").bfloat16()
+tgt = torch.tensor([3, 99, 1000, 5], device="cuda")           # 1000 is outside the 100 classes
+loss = pf.cross_entropy(logits, tgt, vocab_size=100, reduction="sum")
+torch.cuda.synchronize()
+try:
+    _lib.check_device_errors()
+    raise SystemExit("the bad label was not reported")
+except _lib.KernelError as e:
+    assert "code 5" in str(e), e
+ok = pf.cross_entropy(logits, torch.tensor([3, 99, 0, 5], device="cuda"), vocab_size=100, reduction="sum")
+torch.cuda.synchronize()
+_lib.check_device_errors()
+print("bounds-check build ok", float(loss), float(ok))
+"""
+    env = dict(os.environ, PIPPY_BOUNDS_CHECK="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "bounds-check build ok" in res.stdout
