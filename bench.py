@@ -47,13 +47,17 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--microbatches", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (quick checks only)")
+    ap.add_argument("--inner", type=int, default=None,
+                    help="size of the composed configs' second dimension (dp / tp / ep); the rest of the GPUs form the "
+                         "pipeline (quick checks on fewer than 8 GPUs)")
     ap.add_argument("--virtual", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-retune", action="store_true",
                     help="keep the zero-bubble order of the fixed 2:3:2 cost guess instead of rebuilding it from the "
                          "per-stage times measured in the second warm-up step")
-    ap.add_argument("--comm-latency-ms", type=float, default=1.0,
-                    help="assumed time for an activation to reach the next rank, used by the cost-aware order")
+    ap.add_argument("--p2p-gbs", type=float, default=40.0,
+                    help="rate at which the cost-aware order assumes activations reach the next rank (the NCCL "
+                         "point-to-point kernels are capped at two thread blocks per link, far below link speed)")
     ap.add_argument("--sm-reserve", type=int, default=None,
                     help="SMs kept out of the GEMM grid for communication kernels (default: 0 on 1 GPU, 8 otherwise)")
     args = ap.parse_args()
@@ -164,7 +168,7 @@ def build_job(args, world: int, device):
     if args.config == "gpt2-pp4dp2":
         from pippy_b200.models.gpt2 import GPT2Config
 
-        dp = 2 if world % 2 == 0 else 1
+        dp = args.inner or (2 if world % 2 == 0 else 1)
         pp = world // dp
         mesh = init_mesh(pp_size=pp, dp_size=dp)
         cfg = GPT2Config.small()
@@ -182,7 +186,7 @@ def build_job(args, world: int, device):
     if args.config == "llama13b-tp4pp2":
         from pippy_b200.models.llama import LlamaConfig
 
-        tp = 4 if world % 4 == 0 else 2
+        tp = args.inner or (4 if world % 4 == 0 else 2)
         pp = world // tp
         mesh = init_mesh(pp_size=pp, tp_size=tp)
         cfg = LlamaConfig.llama2_13b()
@@ -198,7 +202,7 @@ def build_job(args, world: int, device):
     if args.config == "mixtral-pp2ep4":
         from pippy_b200.models.mixtral import MixtralConfig
 
-        ep = 4 if world % 4 == 0 else 2
+        ep = args.inner or (4 if world % 4 == 0 else 2)
         pp = world // ep
         mesh = init_mesh(pp_size=pp, tp_size=ep)  # the mesh's fastest axis carries the experts
         cfg = MixtralConfig.mixtral_16l()
@@ -300,7 +304,7 @@ def main() -> None:
         loss = pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
         if measure:
             pipe.schedule.record_timing = False
-            retuned = pipe.schedule.retune_from_last_step(comm_latency=args.comm_latency_ms * 1e-3)
+            retuned = pipe.schedule.retune_from_last_step(p2p_bytes_per_s=args.p2p_gbs * 1e9)
     barrier()
     _lib.check_device_errors()
 

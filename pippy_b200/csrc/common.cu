@@ -64,6 +64,15 @@ static int encode_cached(CUtensorMap* tm, const void* ptr, int elem_bytes, int r
   }
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return -1;
+  // The encoder is a driver-API call and needs a context bound to the calling thread.  A thread that has only ever
+  // been told "device 0" (autograd's backward thread on the first GPU: frameworks skip cudaSetDevice when the
+  // target is already the current device) has none until its first runtime call, and the encoder then answers
+  // CUDA_ERROR_INVALID_CONTEXT.  cudaFree(0) binds the primary context; once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(0);
+    context_bound = true;
+  }
   cuuint64_t gdim[3];
   cuuint64_t gstride[2];
   cuuint32_t bx[3];

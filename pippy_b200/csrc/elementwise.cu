@@ -65,9 +65,12 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __rest
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
 // gu: [T, 2F] (gate | up) -> out [T, F] = silu(gate) * up
+// row_limit (optional, device): only rows below *row_limit are processed (buffers sized for a capacity of which the
+// device knows how much is in use)
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
-                                  int F) {
+                                  int F, const int* __restrict__ row_limit) {
   const int vec = F / 8;
+  if (row_limit && *row_limit < T) T = *row_limit;
   const long long total = T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -85,8 +88,10 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
 
 // dgu [T, 2F] from dout [T, F] and gu
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ dgu, long long T, int F) {
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int F,
+                                  const int* __restrict__ row_limit) {
   const int vec = F / 8;
+  if (row_limit && *row_limit < T) T = *row_limit;
   const long long total = T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -233,23 +238,25 @@ int pb_rope(void* qkv, const float* cs, const float* sn, long long T, int S, int
   return (int)cudaGetLastError();
 }
 
-int pb_swiglu_fwd(const void* gu, void* out, long long T, int F, void* stream_) {
+int pb_swiglu_fwd(const void* gu, void* out, long long T, int F, const int* row_limit, void* stream_) {
   using namespace pbe;
   if (F % 8 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
-                                                                     reinterpret_cast<__nv_bfloat16*>(out), T, F);
+                                                                     reinterpret_cast<__nv_bfloat16*>(out), T, F,
+                                                                     row_limit);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
 
-int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int F, void* stream_) {
+int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int F, const int* row_limit,
+                  void* stream_) {
   using namespace pbe;
   if (F % 8 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dout), reinterpret_cast<const __nv_bfloat16*>(gu),
-      reinterpret_cast<__nv_bfloat16*>(dgu), T, F);
+      reinterpret_cast<__nv_bfloat16*>(dgu), T, F, row_limit);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

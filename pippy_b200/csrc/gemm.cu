@@ -798,10 +798,10 @@ int pb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   int r;
   if (!a_mn) r = make_tmap_bf16_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128);
   else r = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64);
-  if (r) return -10;
+  if (r) return -1000 - r;  // tensor map of A refused: -1000 - CUresult (or +1 when the encoder is missing)
   if (!b_mn) r = make_tmap_bf16_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)b_rows);
   else r = make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64);
-  if (r) return -11;
+  if (r) return -2000 - r;  // tensor map of B refused
 
   GemmParams p;
   memset(&p, 0, sizeof(p));

@@ -244,7 +244,7 @@ constexpr int ERR_CAPACITY = 4;
 // count table (row s = what rank s holds); recv[r]: every rank's receive buffer [cap_rows, H]; scale: optional [T*k]
 // fp32.  Outputs on this rank: dst_base[e] = first row of this rank's block inside expert e's group on its owner
 // (what the combine needs), group_rows / group_start [experts_per_rank] = the layout of this rank's own receive
-// buffer (what the grouped GEMM needs).
+// buffer (what the grouped GEMM needs), rows_used = where the last group's padding ends.
 __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
                                                                const int* __restrict__ expert,
                                                                const int* __restrict__ slot,
@@ -255,7 +255,8 @@ __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat
                                                                int E, int experts_per_rank, int cap_rows,
                                                                int* __restrict__ dst_base_out,
                                                                int* __restrict__ group_rows_out,
-                                                               int* __restrict__ group_start_out, Comm c) {
+                                                               int* __restrict__ group_start_out,
+                                                               int* __restrict__ rows_used_out, Comm c) {
   __shared__ __nv_bfloat16* s_recv[MAX_RANKS];
   __shared__ int s_cnt[MAX_RANKS][MAX_EXPERTS];
   __shared__ int s_total[MAX_EXPERTS], s_base[MAX_EXPERTS];
@@ -298,6 +299,8 @@ __global__ void __launch_bounds__(THREADS) moe_dispatch_kernel(const __nv_bfloat
       if (d == c.rank) {
         group_rows_out[e - d * experts_per_rank] = min(s_total[e], max(cap_rows - start, 0));
         group_start_out[e - d * experts_per_rank] = min(start, cap_rows / 256 * 256);
+        // rows of this rank's buffer that hold a group or its padding: what element-wise kernels have to touch
+        if (e == (d + 1) * experts_per_rank - 1) *rows_used_out = min(start + (s_total[e] + 255) / 256 * 256, cap_rows);
       }
     }
   }
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(THREADS) moe_combine_kernel(__nv_bfloat16* __r
                                                               const float* __restrict__ weight,
                                                               __nv_bfloat16* const* __restrict__ y_ptrs,
                                                               __nv_bfloat16* __restrict__ save, int T, int k, int H,
-                                                              int experts_per_rank, Comm c) {
+                                                              int experts_per_rank, int cap_rows, Comm c) {
   __shared__ __nv_bfloat16* s_y[MAX_RANKS];
   if (threadIdx.x < MAX_RANKS) s_y[threadIdx.x] = threadIdx.x < c.world ? y_ptrs[threadIdx.x] : nullptr;
   __syncthreads();
@@ -365,8 +368,13 @@ __global__ void __launch_bounds__(THREADS) moe_combine_kernel(__nv_bfloat16* __r
       if (j < k) {
         const long long a = t * k + j;
         const int e = expert[a];
-        rows[j] = reinterpret_cast<const uint4*>(s_y[e / experts_per_rank] + ((long long)dst_base[e] + slot[a]) * H);
+        long long row = (long long)dst_base[e] + slot[a];
         w[j] = weight ? weight[a] : 1.f;
+        if (row >= cap_rows) {  // the dispatch dropped this row (receive buffer full, error word set): contributes 0
+          row = 0;
+          w[j] = 0.f;
+        }
+        rows[j] = reinterpret_cast<const uint4*>(s_y[e / experts_per_rank] + row * H);
       }
     }
     // peer loads take microseconds: every lane issues k * UNROLL of them before it touches the first result
@@ -477,8 +485,8 @@ int pb_moe_route_bwd(const float* probs, const int* topi, const float* topw, con
 // A receive buffer that would overflow `cap_rows` sets the device error word to 4 and drops the rows beyond it.
 int pb_moe_dispatch(const void* x, const int* expert, const int* slot, const int* counts, const float* scale,
                     void* recv_ptrs_dev, void* cnt_ptrs_dev, int T, int k, int H, int E, int experts_per_rank,
-                    int cap_rows, int* dst_base_out, int* group_rows_out, int* group_start_out, int** flags,
-                    int* counter, int* err, int rank, int world, int epoch, int ctas, void* stream_) {
+                    int cap_rows, int* dst_base_out, int* group_rows_out, int* group_start_out, int* rows_used_out,
+                    int** flags, int* counter, int* err, int rank, int world, int epoch, int ctas, void* stream_) {
   using namespace pbmoe;
   if (H % 8 != 0 || world > MAX_RANKS || E > MAX_EXPERTS || E % world != 0 || experts_per_rank * world != E) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -487,14 +495,14 @@ int pb_moe_dispatch(const void* x, const int* expert, const int* slot, const int
   moe_dispatch_kernel<<<ctas, THREADS, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), expert, slot, counts, scale,
       reinterpret_cast<__nv_bfloat16* const*>(recv_ptrs_dev), reinterpret_cast<int* const*>(cnt_ptrs_dev), T, k, H, E,
-      experts_per_rank, cap_rows, dst_base_out, group_rows_out, group_start_out,
+      experts_per_rank, cap_rows, dst_base_out, group_rows_out, group_start_out, rows_used_out,
       make_comm(flags, counter, err, rank, world, epoch));
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
 
 int pb_moe_combine(void* out, const int* expert, const int* slot, const int* dst_base, const float* weight,
-                   void* y_ptrs_dev, void* save, int T, int k, int H, int experts_per_rank, int** flags,
+                   void* y_ptrs_dev, void* save, int T, int k, int H, int experts_per_rank, int cap_rows, int** flags,
                    int* counter, int* err, int rank, int world, int epoch, int ctas, void* stream_) {
   using namespace pbmoe;
   if (H % 8 != 0 || world > MAX_RANKS || k > MAX_TOPK) return -1;
@@ -504,7 +512,7 @@ int pb_moe_combine(void* out, const int* expert, const int* slot, const int* dst
   moe_combine_kernel<<<ctas, THREADS, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(out), expert, slot, dst_base,
                                                    weight, reinterpret_cast<__nv_bfloat16* const*>(y_ptrs_dev),
                                                    reinterpret_cast<__nv_bfloat16*>(save), T, k, H, experts_per_rank,
-                                                   make_comm(flags, counter, err, rank, world, epoch));
+                                                   cap_rows, make_comm(flags, counter, err, rank, world, epoch));
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

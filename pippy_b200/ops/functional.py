@@ -271,7 +271,7 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
 # ------------------------------------------------------------------------------------------------
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gu):
+    def forward(ctx, gu, row_limit=None):
         F2 = gu.shape[-1]
         g2 = gu.reshape(-1, F2)
         if not g2.is_contiguous():
@@ -279,10 +279,11 @@ class _SwiGLUFn(torch.autograd.Function):
         out = torch.empty(g2.shape[0], F2 // 2, device=gu.device, dtype=gu.dtype)
         _lib.check(
             _lib.lib().pb_swiglu_fwd(_lib.ptr(g2), _lib.ptr(out), _lib.c_ll(g2.shape[0]), _lib.c_int(F2 // 2),
-                                     _lib.stream_ptr()),
+                                     _lib.ptr(row_limit), _lib.stream_ptr()),
             "pb_swiglu_fwd",
         )
         ctx.save_for_backward(g2)
+        ctx.row_limit = row_limit
         ctx.shape = gu.shape
         return out.view(*gu.shape[:-1], F2 // 2)
 
@@ -295,16 +296,18 @@ class _SwiGLUFn(torch.autograd.Function):
         dgu = torch.empty_like(g2)
         _lib.check(
             _lib.lib().pb_swiglu_bwd(_lib.ptr(d2), _lib.ptr(g2), _lib.ptr(dgu), _lib.c_ll(g2.shape[0]),
-                                     _lib.c_int(g2.shape[1] // 2), _lib.stream_ptr()),
+                                     _lib.c_int(g2.shape[1] // 2), _lib.ptr(ctx.row_limit), _lib.stream_ptr()),
             "pb_swiglu_bwd",
         )
-        return dgu.view(ctx.shape)
+        return dgu.view(ctx.shape), None
 
 
-def swiglu(gate_up):
-    """``silu(gate) * up`` for ``gate_up = [..., gate | up]`` (two equal halves on the last dim)."""
+def swiglu(gate_up, row_limit=None):
+    """``silu(gate) * up`` for ``gate_up = [..., gate | up]`` (two equal halves on the last dim).  ``row_limit``
+    (an int32 device scalar, kernel path only) restricts the work to the first ``row_limit`` rows of a buffer that
+    is sized for a capacity; the other rows of the result (and of the gradient) are left as allocated."""
     if _use_kernels(gate_up):
-        return _SwiGLUFn.apply(gate_up)
+        return _SwiGLUFn.apply(gate_up, row_limit)
     g, u = gate_up.chunk(2, dim=-1)
     return F.silu(g) * u
 

@@ -60,7 +60,11 @@ def gemm(
         _lib.ptr(aux), _lib.c_int(act), _lib.c_int(int(out_fp32)), _lib.c_int(int(accumulate)),
         _lib.c_int(variant), _lib.ptr(_lib.err_word(a.device)), _lib.stream_ptr(),
     )
-    _lib.check(rc, "pb_gemm_bf16")
+    if rc != 0:
+        raise _lib.KernelError(
+            f"pb_gemm_bf16 failed with code {rc}: a {tuple(a.shape)} strides {a.stride()} ptr%16={a.data_ptr() % 16}, "
+            f"b {tuple(b.shape)} strides {b.stride()} ptr%16={b.data_ptr() % 16}, out {tuple(out.shape)} "
+            f"{out.dtype} strides {out.stride()}, a_mn={a_mn} b_mn={b_mn}, M={M} N={N} K={K}")
     return out
 
 

@@ -94,7 +94,7 @@ class EPContext:
             _lib.ptr(self.recv_ptrs), _lib.ptr(self.cnt_ptrs), _lib.c_int(T), _lib.c_int(self.top_k),
             _lib.c_int(self.hidden), _lib.c_int(self.n_experts), _lib.c_int(self.experts_per_rank),
             _lib.c_int(self.capacity), _lib.ptr(plan.dst_base), _lib.ptr(plan.group_rows),
-            _lib.ptr(plan.group_start), self._flags(self.flags_d), _lib.ptr(self.counter),
+            _lib.ptr(plan.group_start), _lib.ptr(plan.rows_used), self._flags(self.flags_d), _lib.ptr(self.counter),
             _lib.ptr(_lib.err_word(x.device)), _lib.c_int(self.rank), _lib.c_int(self.world),
             _lib.c_int(self.epoch_d), _lib.c_int(self.ctas), _lib.stream_ptr())
         _lib.check(rc, "pb_moe_dispatch")
@@ -105,7 +105,8 @@ class EPContext:
         rc = _lib.lib().pb_moe_combine(
             _lib.ptr(out), _lib.ptr(plan.expert), _lib.ptr(plan.slot), _lib.ptr(plan.dst_base), _lib.ptr(weight),
             _lib.ptr(self.y_ptrs), _lib.ptr(save), _lib.c_int(T), _lib.c_int(self.top_k), _lib.c_int(self.hidden),
-            _lib.c_int(self.experts_per_rank), self._flags(self.flags_c), _lib.ptr(self.counter[1:]),
+            _lib.c_int(self.experts_per_rank), _lib.c_int(self.capacity), self._flags(self.flags_c),
+            _lib.ptr(self.counter[1:]),
             _lib.ptr(_lib.err_word(out.device)), _lib.c_int(self.rank), _lib.c_int(self.world),
             _lib.c_int(self.epoch_c), _lib.c_int(self.ctas), _lib.stream_ptr())
         _lib.check(rc, "pb_moe_combine")
@@ -126,6 +127,7 @@ class _Plan:
         self.dst_base = torch.empty(E, dtype=torch.int32, device=dev)     # filled by the dispatch kernel
         self.group_rows = torch.zeros(ep.experts_per_rank, dtype=torch.int32, device=dev)
         self.group_start = torch.zeros(ep.experts_per_rank, dtype=torch.int32, device=dev)
+        self.rows_used = torch.zeros(1, dtype=torch.int32, device=dev)  # rows that hold a group or its padding
 
 
 class _RouteFn(torch.autograd.Function):
@@ -335,7 +337,7 @@ class MoEFeedForward(nn.Module):
             if self.aux_coef:
                 x = _AuxLossInject.apply(x, aux * self.aux_coef)
             rows = _DispatchFn.apply(x, plan)
-            h = pf.swiglu(_GroupedLinearFn.apply(rows, self.w_gate_up, plan))
+            h = pf.swiglu(_GroupedLinearFn.apply(rows, self.w_gate_up, plan), row_limit=plan.rows_used)
             y_local = _GroupedLinearFn.apply(h, self.w_down, plan)
             return _CombineFn.apply(y_local, topw, plan, T)
         # dense reference path (one rank holds every expert): plain PyTorch statement of the same layer

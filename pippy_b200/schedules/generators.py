@@ -216,7 +216,8 @@ def zero_bubble_costed(
     first, then a forward while the in-flight limit allows, weight gradients in the gaps), but on a continuous
     event-driven timeline, so that a heavier stage (the one with the LM head and the loss) and an I : W ratio that
     differs from the 3 : 2 guess shift the order instead of showing up as idle time.  A value produced on another
-    rank becomes usable ``comm_latency`` after its producer ends.  With ``placement`` (stage -> rank) the forward and
+    rank becomes usable ``comm_latency`` after its producer ends; a dict ``{s: seconds}`` gives the transfer time of
+    the boundary between stages ``s`` and ``s + 1`` (both directions) when boundaries carry different amounts.  With ``placement`` (stage -> rank) the forward and
     input-gradient orders are per stage, nearest the loss first, as in :func:`zero_bubble_placed`."""
     S = P * v if placement is None else len(placement)
     where = (lambda s: s % P) if placement is None else (lambda s: placement[s])
@@ -251,18 +252,21 @@ def zero_bubble_costed(
     out: Schedule = {r: [] for r in range(P)}
     INF = float("inf")
 
-    def ready_at(key, consumer_rank):
+    def latency(boundary):
+        return comm_latency.get(boundary, 0.0) if isinstance(comm_latency, dict) else comm_latency
+
+    def ready_at(key, consumer_rank, boundary):
         t = finish.get(key)
         if t is None:
             return INF
-        return t + (comm_latency if where(key[0]) != consumer_rank else 0.0)
+        return t + (latency(boundary) if where(key[0]) != consumer_rank else 0.0)
 
     def f_ready(s, m, r):
-        return 0.0 if s == 0 else ready_at((s - 1, "F", m), r)
+        return 0.0 if s == 0 else ready_at((s - 1, "F", m), r, s - 1)
 
     def i_ready(s, m, r):
-        t = ready_at((s, "F", m), r)
-        return t if s == S - 1 else max(t, ready_at((s + 1, "I", m), r))
+        t = ready_at((s, "F", m), r, s)
+        return t if s == S - 1 else max(t, ready_at((s + 1, "I", m), r, s))
 
     blocked = set()  # ranks waiting for a producer that nobody has scheduled yet
     while any(left.values()):

@@ -535,15 +535,21 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
         if sorted(costs) != list(range(self.num_stages)):
             raise ValueError(f"costs must cover stages 0..{self.num_stages - 1}")
         self.stage_costs = {int(s): tuple(float(x) for x in c) for s, c in costs.items()}
-        self.comm_latency = float(comm_latency)
+        self.comm_latency = ({int(k): float(v) for k, v in comm_latency.items()} if isinstance(comm_latency, dict)
+                             else float(comm_latency))
         self._build()
 
-    def retune_from_last_step(self, comm_latency: float = 0.0) -> Dict[int, Tuple[float, float, float]]:
+    def retune_from_last_step(self, comm_latency=0.0, p2p_bytes_per_s: Optional[float] = None):
         """Collective over the pipeline group: gathers every rank's measured per-stage F / I / W means of the last
-        step (which must have run with ``record_timing``) and rebuilds the order from them."""
+        step (which must have run with ``record_timing``) and rebuilds the order from them.  With
+        ``p2p_bytes_per_s`` the transfer time of every stage boundary is derived from the bytes the producing stage
+        sends (boundaries inside a layer carry two tensors) instead of one ``comm_latency`` for all."""
         if self.last_step_stats is None:
             raise RuntimeError("run one step with record_timing=True first")
-        mine = self.last_step_stats["per_stage_op_mean_s"]
+        mine = dict(self.last_step_stats["per_stage_op_mean_s"])
+        for st in self._stages:
+            nbytes = sum(m.shape.numel() * torch.empty((), dtype=m.dtype).element_size() for m in st.output_metas)
+            mine[f"{st.stage_index}:bytes"] = float(nbytes)
         tables: List[Optional[dict]] = [None] * self.pp_group_size
         if self.pp_group_size > 1:
             dist.all_gather_object(tables, mine, group=self._stages[0].group)
@@ -558,6 +564,8 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
             if f is None or i is None or w is None:
                 raise RuntimeError(f"no measured F / I / W time for stage {s}: the last step did not run a split backward")
             costs[s] = (f, i, w)
+        if p2p_bytes_per_s:
+            comm_latency = {s: merged.get(f"{s}:bytes", 0.0) / p2p_bytes_per_s for s in range(self.num_stages - 1)}
         self.set_stage_costs(costs, comm_latency)
         return costs
 

@@ -243,7 +243,7 @@ def build_mixtral_pipeline(
     weight_decay: float = 0.1,
     seed: int = 0,
     record_timing: bool = False,
-    capacity_factor: float = 1.5,
+    capacity_factor: Optional[float] = None,
 ) -> Pipeline:
     """Mixtral stages for a PP x EP layout. ``global_batch`` is the batch of ONE expert-parallel rank (EP ranks are
     data-parallel replicas for the dense layers): dense gradients are averaged over ``ep_group`` with the fused
@@ -262,7 +262,10 @@ def build_mixtral_pipeline(
     ep = None
     if device.type == "cuda" and (ep_size > 1 or ep_group is not None or not dist.is_initialized()):
         ep = EPContext(ep_group, max_tokens=mb * seq_len, hidden=cfg.dim, top_k=cfg.top_k, n_experts=cfg.n_experts,
-                       device=device, capacity_factor=capacity_factor)
+                       device=device,
+                       # default: room for the worst case (every rank sends everything here), so no routing can
+                       # overflow; only the rows in use are computed on, the rest is address space
+                       capacity_factor=float(ep_size) if capacity_factor is None else capacity_factor)
     stages: List[ManualPipelineStage] = []
     dense, experts = [], []
     for k in range(virtual_stages):
