@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--no-retune", action="store_true",
                     help="keep the zero-bubble order of the fixed 2:3:2 cost guess instead of rebuilding it from the "
                          "per-stage times measured in the second warm-up step")
+    ap.add_argument("--extra-in-flight", type=int, default=None,
+                    help="upper limit of microbatches beyond the 1F1B depth that the cost-aware order may keep in "
+                         "flight per rank (default: derived from the memory left after the first steps)")
     ap.add_argument("--p2p-gbs", type=float, default=40.0,
                     help="rate at which the cost-aware order assumes activations reach the next rank (the NCCL "
                          "point-to-point kernels are capped at two thread blocks per link, far below link speed)")
@@ -304,7 +307,18 @@ def main() -> None:
         loss = pipe.train_step(dev_ids[i % n_sets], dev_lbl[i % n_sets])
         if measure:
             pipe.schedule.record_timing = False
-            retuned = pipe.schedule.retune_from_last_step(p2p_bytes_per_s=args.p2p_gbs * 1e9)
+            # Memory decides how many extra microbatches a rank may keep in flight: what the step needed beyond its
+            # resident state, per microbatch-stage of the current depth, against what is left below 85 % of the GPU.
+            torch.cuda.synchronize()
+            peak, resident = torch.cuda.max_memory_allocated(), torch.cuda.memory_allocated()
+            depth = (virtual - 1) * world + (world - 1 - rank) + 1
+            per_unit = max(peak - resident, 1) / depth
+            room = 0.85 * torch.cuda.mem_get_info()[1] - torch.cuda.max_memory_reserved()  # reserved: with fragmentation
+            allowed = int(min(16, max(0, room // per_unit)))
+            extra = int(-max_over_ranks(-float(allowed)))  # the minimum over ranks: every rank builds the same order
+            retuned = pipe.schedule.retune_from_last_step(p2p_bytes_per_s=args.p2p_gbs * 1e9,
+                                                          max_extra_in_flight=max(extra, 2) if args.extra_in_flight
+                                                          is None else args.extra_in_flight)
     barrier()
     _lib.check_device_errors()
 
@@ -441,7 +455,8 @@ def main() -> None:
                 "parallelism": info["parallelism"],
                 "schedule": schedule,
                 "sm_reserve": sm_reserve,
-                "order": ("measured per-stage costs" if retuned is not None else "generator defaults"),
+                "order": ("measured per-stage costs, up to %d extra microbatches in flight"
+                          % pipe.schedule.max_extra_in_flight if retuned is not None else "generator defaults"),
                 "optimizer": "AdamW lr 3e-4 (fused, fp32 moments, fp32 gradient accumulation)",
                 "l2": "inputs larger than L2 (13.5 GB of weights and GBs of activations stream every step)",
             },

@@ -511,6 +511,9 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
         self.extra_in_flight = extra_in_flight
         self.stage_costs: Optional[Dict[int, Tuple[float, float, float]]] = None
         self.comm_latency = 0.0
+        # how many microbatches beyond the 1F1B depth the cost-aware order may keep in flight per rank (each costs
+        # one stage's activations); deep pipelines need several to cover the round trip of the first gradient
+        self.max_extra_in_flight = 2
         if self._num_local > 1 and n_microbatches % self.pp_group_size != 0:
             raise ValueError(
                 f"interleaved zero-bubble requires the number of microbatches ({n_microbatches}) to be a multiple of "
@@ -521,8 +524,11 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
         if not self._has_backward:
             return generators.interleaved_1f1b(self.pp_group_size, self._num_local, self._n_microbatches, False)
         if self.stage_costs is not None:
+            extras = tuple(e for e in (0, 1, 2, 4, 6, 8, 12, 16) if e <= self.max_extra_in_flight)
             return generators.tuned_zero_bubble_costed(
-                self.pp_group_size, self._num_local, self._n_microbatches, self.stage_costs, self.comm_latency
+                self.pp_group_size, self._num_local, self._n_microbatches, self.stage_costs, self.comm_latency,
+                extra_in_flight=extras,
+                pending_w=(self.pp_group_size, 2 * self.pp_group_size, 4 * self.pp_group_size),
             )
         return generators.zero_bubble(
             self.pp_group_size, self._num_local, self._n_microbatches, self.max_pending_w, self.extra_in_flight
@@ -539,7 +545,8 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
                              else float(comm_latency))
         self._build()
 
-    def retune_from_last_step(self, comm_latency=0.0, p2p_bytes_per_s: Optional[float] = None):
+    def retune_from_last_step(self, comm_latency=0.0, p2p_bytes_per_s: Optional[float] = None,
+                              max_extra_in_flight: Optional[int] = None):
         """Collective over the pipeline group: gathers every rank's measured per-stage F / I / W means of the last
         step (which must have run with ``record_timing``) and rebuilds the order from them.  With
         ``p2p_bytes_per_s`` the transfer time of every stage boundary is derived from the bytes the producing stage
@@ -566,6 +573,8 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
             costs[s] = (f, i, w)
         if p2p_bytes_per_s:
             comm_latency = {s: merged.get(f"{s}:bytes", 0.0) / p2p_bytes_per_s for s in range(self.num_stages - 1)}
+        if max_extra_in_flight is not None:
+            self.max_extra_in_flight = int(max_extra_in_flight)  # must be the same on every rank
         self.set_stage_costs(costs, comm_latency)
         return costs
 
