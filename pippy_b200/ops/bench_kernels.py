@@ -4,7 +4,10 @@
     python -m pippy_b200.ops.bench_kernels attention
     python -m pippy_b200.ops.bench_kernels attention-once     # two forward+backward calls on a small case, for ncu
     python -m pippy_b200.ops.bench_kernels gemm-once          # three launches of one GEMM, for ncu
-    python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe
+    python -m pippy_b200.ops.bench_kernels grouped            # grouped expert GEMMs vs a loop of plain GEMMs / cuBLAS
+    python -m pippy_b200.ops.bench_kernels grouped-once       # three grouped launches on a small case, for ncu
+    python -m pippy_b200.ops.bench_kernels route              # MoE router kernels vs the eager statement
+    python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe | peer-copy
 
 Library rates (cuBLAS via torch.matmul, SDPA) are printed beside ours for scale.
 """
@@ -155,7 +158,7 @@ def bench_tp():
         ms_f, ms_b = timed(lambda: tp.ag_gemm(x, w)), timed(baseline)
         flops = 2 * T * n_local * d
         wire = (W - 1) * rows * d * 2
-        roof = max(flops / 1642e12, wire / 770e9) * 1e3
+        roof = max(flops / 1642e12, wire / 900e9) * 1e3  # measured cuBLAS burst vs NVLink nominal per direction
         if rank == 0:
             print(f"all-gather->GEMM {name:8s} [{rows}->{T},{d}]x[{n_local},{d}]: fused {ms_f:.3f} ms, NCCL+cuBLAS "
                   f"{ms_b:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_f:.2f} of roofline")
@@ -172,7 +175,7 @@ def bench_tp():
         ms_f, ms_b = timed(lambda: tp.gemm_rs(x, w)), timed(baseline)
         flops = 2 * T * d * k_local
         wire = (W - 1) * rows * d * 2
-        roof = max(flops / 1642e12, wire / 770e9) * 1e3
+        roof = max(flops / 1642e12, wire / 900e9) * 1e3  # measured cuBLAS burst vs NVLink nominal per direction
         if rank == 0:
             print(f"GEMM->reduce-scatter {name:5s} [{T},{k_local}]->[{rows},{d}]: fused {ms_f:.3f} ms, cuBLAS+NCCL "
                   f"{ms_b:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_f:.2f} of roofline")
@@ -209,6 +212,48 @@ def _dist_timed(fn, iters=10):
     return t.item()
 
 
+NVLINK_NOMINAL = 900e9  # bytes/s per direction per GPU (NVLink 5); the rooflines below are quoted against this
+
+
+def bench_peer_copy():
+    """Measured peer-read bandwidth: every rank pulls the next rank's buffer with the package's peer all-gather kernel
+    (plain 16-byte loads over NVLink, 4 in flight per thread).  With 2 ranks all of it crosses one direction of the link.
+    Launch with: python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels peer-copy"""
+    import ctypes
+
+    import torch.distributed as dist
+
+    from ..comm.symm import SymmetricBuffer
+    from . import _lib
+
+    rank, W = _dist_setup()
+    for nbytes in (64 << 20, 256 << 20, 1 << 30):
+        src = SymmetricBuffer(nbytes, None, torch.device("cuda", torch.cuda.current_device()))
+        flags = SymmetricBuffer(4096, None, torch.device("cuda", torch.cuda.current_device()))
+        dst = torch.empty(W * nbytes, dtype=torch.uint8, device="cuda")
+        counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        flg = (ctypes.POINTER(ctypes.c_int) * W)(
+            *[ctypes.cast(ctypes.c_void_p(p_), ctypes.POINTER(ctypes.c_int)) for p_ in flags.ptrs])
+        epoch = [0]
+        for ctas in (32, 148, 296):
+            def run():
+                epoch[0] += 1
+                _lib.check(_lib.lib().pb_peer_allgather(
+                    _lib.ptr(dst), src.pointer_array(), flg, _lib.ptr(counter), _lib.ptr(_lib.err_word()),
+                    _lib.c_ll(nbytes), _lib.c_int(rank), _lib.c_int(W), _lib.c_int(epoch[0]), _lib.c_int(ctas),
+                    _lib.stream_ptr()), "pb_peer_allgather")
+
+            ms = _dist_timed(run)
+            if rank == 0:
+                pulled = (W - 1) * nbytes
+                print(f"peer all-gather {nbytes >> 20} MiB per rank, {W} ranks, {ctas} CTAs: {ms:.3f} ms, "
+                      f"{pulled / ms / 1e6:.0f} GB/s pulled over NVLink per GPU ({pulled / ms / 1e6 / 900:.2f} of the "
+                      f"900 GB/s nominal per direction)")
+        del dst
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def bench_dp():
     """Fused cast + scale + all-reduce of a stage's fp32 gradient buffer (bf16 on the wire) against NCCL.
     Launch with: python -m torch.distributed.run --nproc-per-node W -m pippy_b200.ops.bench_kernels dp"""
@@ -243,11 +288,13 @@ def bench_dp():
         ms_f, ms_16, ms_32 = _dist_timed(fused), _dist_timed(nccl_bf16), _dist_timed(nccl_fp32)
         # two-shot all-reduce: every rank sends and receives (W - 1) / W of the bf16 buffer twice
         wire = 2 * (W - 1) / W * n * 2
-        roof = max(wire / 770e9, (n * 4 * 2) / 6549e9) * 1e3  # NVLink vs reading + writing the fp32 buffer in HBM
+        # the slower of NVLink (per direction: (W - 1) / W of the bf16 bucket in each of the two shots) and HBM (the
+        # fp32 bucket read and written once)
+        roof = max(wire / 2 / NVLINK_NOMINAL, (n * 4 * 2) / 6549e9) * 1e3
         if rank == 0:
             print(f"DP all-reduce {n / 1e6:7.1f} M grads, {W} ranks: fused {ms_f:.3f} ms, NCCL bf16 wire (scale, cast, "
-                  f"all-reduce, cast back) {ms_16:.3f} ms, NCCL fp32 {ms_32:.3f} ms, roofline {roof:.3f} ms -> "
-                  f"{roof / ms_f:.2f} of roofline")
+                  f"all-reduce, cast back) {ms_16:.3f} ms, NCCL fp32 {ms_32:.3f} ms, roofline {roof:.3f} ms (NVLink at "
+                  f"900 GB/s per direction vs HBM at the measured 6549 GB/s) -> {roof / ms_f:.2f} of roofline")
         del red, flat
     dist.barrier()
     dist.destroy_process_group()
@@ -305,7 +352,7 @@ def bench_moe():
     ms_fc, ms_lc = _dist_timed(fused_combine), _dist_timed(lib_combine)
     rows_remote = T * K * (W - 1) / W  # expected rows that leave this rank
     wire = rows_remote * H * 2
-    roof = max(wire / 770e9, (T * K * H * 2 * 2) / 6549e9) * 1e3
+    roof = max(wire / NVLINK_NOMINAL, (T * K * H * 2 * 2) / 6549e9) * 1e3
     if rank == 0:
         print(f"MoE dispatch T{T} top-{K} H{H} E{E}, {W} ranks: fused {ms_fd:.3f} ms, all_to_all_single + gather "
               f"{ms_ld:.3f} ms, roofline {roof:.3f} ms -> {roof / ms_fd:.2f} of roofline")
@@ -315,10 +362,97 @@ def bench_moe():
     dist.destroy_process_group()
 
 
+def _grouped_case(rows_per_group, dim, ffn2):
+    """Expert-grouped activations with group starts on multiples of 256 rows, as the MoE dispatch lays them out."""
+    from ..parallel.ep import EPContext, _Plan
+
+    G = len(rows_per_group)
+    starts, pos = [], 0
+    for r in rows_per_group:
+        starts.append(pos)
+        pos += (r + 255) // 256 * 256
+    ep = EPContext(None, max_tokens=max(pos // 2, 256), hidden=dim, top_k=2, n_experts=G, capacity_factor=1.0)
+    plan = _Plan(ep, 1)
+    plan.group_rows = torch.tensor(rows_per_group, dtype=torch.int32, device="cuda")
+    plan.group_start = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    cap = pos
+    x = torch.randn(cap, dim, device="cuda").bfloat16()
+    w = (torch.randn(G, ffn2, dim, device="cuda") * 0.02).bfloat16()
+    return plan, x, w, starts, cap
+
+
+def bench_grouped():
+    """One grouped launch over the local experts of a Mixtral layer (2 experts per rank at EP4, uneven groups) against
+    the same work as a loop of this package's plain GEMM and as a loop of cuBLAS GEMMs."""
+    from ..parallel.ep import grouped_gemm
+    from .gemm import gemm
+
+    dim, ffn2 = 4096, 28672
+    for rows in ([4096, 4096], [5200, 3000], [1024, 1024, 1024, 1024, 1024, 1024, 1024, 1024]):
+        plan, x, w, starts, cap = _grouped_case(rows, dim, ffn2)
+        G = len(rows)
+        y = torch.empty(cap, ffn2, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn(cap, ffn2, device="cuda").bfloat16()
+        dx = torch.empty(cap, dim, device="cuda", dtype=torch.bfloat16)
+        dw = torch.zeros(G, ffn2, dim, device="cuda", dtype=torch.float32)
+        flops = 2.0 * sum(rows) * dim * ffn2
+
+        def loop_fwd():
+            for g_, (s0, r) in enumerate(zip(starts, rows)):
+                gemm(x[s0:s0 + r], w[g_], out=y[s0:s0 + r])
+
+        def loop_cublas():
+            for g_, (s0, r) in enumerate(zip(starts, rows)):
+                torch.matmul(x[s0:s0 + r], w[g_].t(), out=y[s0:s0 + r])
+
+        ms_f = _time(lambda: grouped_gemm(1, x, w, y, ffn2, dim, plan))
+        ms_d = _time(lambda: grouped_gemm(1, dy, w, dx, dim, ffn2, plan, b_mn=True))
+        ms_w = _time(lambda: grouped_gemm(2, dy, x, dw, dim, cap, plan, accumulate=True))
+        ms_l, ms_c = _time(loop_fwd), _time(loop_cublas)
+        print(f"grouped GEMM rows {rows} x [{dim} -> {ffn2}]: fwd {ms_f:.3f} ms {flops / ms_f / 1e9:.0f} TFLOP/s, dgrad "
+              f"{ms_d:.3f} ms {flops / ms_d / 1e9:.0f}, wgrad (fp32 accumulate) {ms_w:.3f} ms {flops / ms_w / 1e9:.0f}; "
+              f"fwd as a loop of plain GEMMs {ms_l:.3f} ms, as a loop of cuBLAS GEMMs {ms_c:.3f} ms")
+
+
+def grouped_once():
+    """Three grouped forward launches on a small case (operands 40 + 50 MB per launch, output 170 MB), for ncu."""
+    from ..parallel.ep import grouped_gemm
+
+    plan, x, w, starts, cap = _grouped_case([2300, 1500], 2048, 12288)
+    y = torch.empty(cap, 12288, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        grouped_gemm(1, x, w, y, 12288, 2048, plan)
+    torch.cuda.synchronize()
+    print("grouped-once done", float(y[:2300].float().abs().mean()))
+
+
+def bench_route():
+    """Router kernels (softmax, top-2, weights, aux loss, positions: two launches) against the eager statement."""
+    from ..parallel.ep import EPContext, _Plan, _RouteFn
+
+    T, E, k = 8192, 8, 2
+    ep = EPContext(None, max_tokens=T, hidden=64, top_k=k, n_experts=E)
+    logits = torch.randn(T, E, device="cuda").bfloat16()
+    plan = _Plan(ep, T)
+
+    def eager():
+        probs = logits.float().softmax(-1)
+        w, i = probs.topk(k, dim=-1)
+        w = w / w.sum(-1, keepdim=True)
+        share = torch.zeros(E, device="cuda").scatter_add_(0, i.reshape(-1), torch.ones(T * k, device="cuda")) / (T * k)
+        return w, i, E * (share * probs.mean(0)).sum()
+
+    ms_k = _time(lambda: _RouteFn.apply(logits, plan, E, k))
+    ms_e = _time(eager)
+    print(f"MoE router T{T} E{E} top-{k}: kernels {ms_k * 1e3:.1f} us (incl. positions and counts), eager softmax/topk/"
+          f"scatter_add {ms_e * 1e3:.1f} us (without positions)")
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "gemm-once": gemm_once, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
-     "dp": bench_dp, "moe": bench_moe}[what]()
+     "dp": bench_dp, "moe": bench_moe, "peer-copy": bench_peer_copy, "grouped": bench_grouped, "grouped-once": grouped_once,
+     "route": bench_route}[what]()
     from . import _lib
 
     _lib.check_device_errors()
