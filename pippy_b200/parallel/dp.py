@@ -24,8 +24,11 @@ from ..utils import streamcheck
 
 
 class GradReducer:
-    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 96,
+    def __init__(self, flat: FlatParams, dp_group: Optional[dist.ProcessGroup], max_ctas: int = 296,
                  average: bool = True):
+        """``max_ctas`` bounds the kernel's grid (two thread blocks per SM by default: the three passes are
+        bandwidth-bound and need the parallelism; the blocks need not be resident together, so a grid larger than
+        what fits beside a running GEMM only waits its turn)."""
         self.flat = flat
         self.group = dp_group
         self.world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
