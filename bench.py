@@ -311,13 +311,13 @@ def main() -> None:
         if measure:
             pipe.schedule.record_timing = False
             # Memory decides how many extra microbatches a rank may keep in flight: what the step needed beyond its
-            # resident state, per microbatch-stage of the current depth, against what is left below 85 % of the GPU.
+            # resident state, per microbatch-stage of the current depth, against what is left below 80 % of the GPU (at most 8 more).
             torch.cuda.synchronize()
             peak, resident = torch.cuda.max_memory_allocated(), torch.cuda.memory_allocated()
             depth = (virtual - 1) * world + (world - 1 - rank) + 1
             per_unit = max(peak - resident, 1) / depth
-            room = 0.85 * torch.cuda.mem_get_info()[1] - torch.cuda.max_memory_reserved()  # reserved: with fragmentation
-            allowed = int(min(16, max(0, room // per_unit)))
+            room = 0.80 * torch.cuda.mem_get_info()[1] - torch.cuda.max_memory_reserved()  # reserved: with fragmentation
+            allowed = int(min(8, max(0, room // per_unit)))
             extra = int(-max_over_ranks(-float(allowed)))  # the minimum over ranks: every rank builds the same order
             retuned = pipe.schedule.retune_from_last_step(p2p_bytes_per_s=args.p2p_gbs * 1e9,
                                                           max_extra_in_flight=max(extra, 2) if args.extra_in_flight

@@ -528,7 +528,8 @@ class ScheduleInterleavedZeroBubble(PipelineScheduleMulti):
             return generators.tuned_zero_bubble_costed(
                 self.pp_group_size, self._num_local, self._n_microbatches, self.stage_costs, self.comm_latency,
                 extra_in_flight=extras,
-                pending_w=(self.pp_group_size, 2 * self.pp_group_size, 4 * self.pp_group_size),
+                # parked weight-gradient passes hold their operands: never more of them than the default order parks
+                pending_w=(self.pp_group_size, 2 * self.pp_group_size),
             )
         return generators.zero_bubble(
             self.pp_group_size, self._num_local, self._n_microbatches, self.max_pending_w, self.extra_in_flight
