@@ -166,6 +166,7 @@ def build_gpt2_pipeline(
     weight_decay: float = 0.1,
     seed: int = 0,
     record_timing: bool = False,
+    balance: bool = True,
 ) -> Pipeline:
     """GPT-2 stages + schedule + fused optimizer for this rank; ``global_batch`` is the batch of ONE data-parallel
     replica. With ``dp_group`` the stage gradients are reduced by the fused NVLink all-reduce as each stage
@@ -193,7 +194,7 @@ def build_gpt2_pipeline(
     last_rank = placement[num_stages - 1] if placement is not None else (num_stages - 1) % pp_size
     for s in held:
         torch.manual_seed(seed + s)
-        module = build_gpt2_stage(cfg, s, num_stages, device=device, dtype=dtype)
+        module = build_gpt2_stage(cfg, s, num_stages, device=device, dtype=dtype, balance=balance)
         inp = (torch.empty(mb, seq_len, dtype=torch.int64, device="meta") if s == 0
                else torch.empty(mb, seq_len, cfg.dim, dtype=dtype, device="meta"))
         out = (torch.empty(mb, seq_len, cfg.padded_vocab, dtype=dtype, device="meta") if s == num_stages - 1
