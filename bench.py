@@ -47,8 +47,8 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--microbatches", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (quick checks only)")
-    ap.add_argument("--even-layers", action="store_true",
-                    help="gpt2 config: split the blocks evenly over the stages instead of weighing the LM head")
+    ap.add_argument("--weigh-head", action="store_true",
+                    help="gpt2 config: give the stage with the LM head fewer blocks (measured slower: launch-bound)")
     ap.add_argument("--inner", type=int, default=None,
                     help="size of the composed configs' second dimension (dp / tp / ep); the rest of the GPUs form the "
                          "pipeline (quick checks on fewer than 8 GPUs)")
@@ -186,7 +186,7 @@ def build_job(args, world: int, device):
         virtual = 1 if schedule in ("gpipe", "1f1b") else args.virtual
         pipe = train.build_gpt2_pipeline(cfg, args.batch // dp, args.seq, args.microbatches, device, schedule=schedule,
                                          virtual_stages=virtual, group=mesh.pp_group, dp_group=mesh.dp_group,
-                                         balance=not args.even_layers)
+                                         balance=args.weigh_head)
         d, L, V = cfg.dim, cfg.n_layers, cfg.vocab_size
         flops = 6.0 * (L * 12 * d * d + V * d) + 3.0 * L * 2 * args.seq * d
         return pipe, dict(cfg=cfg, model=f"GPT-2 small ({L}L, d{d}, vocab {V}, tied embedding / LM head)",

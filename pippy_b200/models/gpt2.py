@@ -124,7 +124,11 @@ def gpt2_layer_split(cfg: GPT2Config, num_stages: int, head_layers: float = 2.0)
 
 
 def build_gpt2_stage(cfg: GPT2Config, stage: int, num_stages: int, device=None, dtype=torch.bfloat16,
-                     balance: bool = True) -> GPT2Stage:
+                     balance: bool = False) -> GPT2Stage:
+    """``balance`` weighs the LM head when splitting the blocks (:func:`gpt2_layer_split`).  Off by default: at
+    GPT-2 small's size a stage's time is the host's launch time, not the GPU's, and the measured step got slower
+    with it (4 GPUs, PP4, 16 microbatches of 2 x 1024 tokens: 53.1 ms even, 59.5 ms weighted; the first rank, which
+    also feeds the inputs, became the slowest)."""
     if balance:
         counts = gpt2_layer_split(cfg, num_stages)
         start = sum(counts[:stage])

@@ -166,7 +166,7 @@ def build_gpt2_pipeline(
     weight_decay: float = 0.1,
     seed: int = 0,
     record_timing: bool = False,
-    balance: bool = True,
+    balance: bool = False,
 ) -> Pipeline:
     """GPT-2 stages + schedule + fused optimizer for this rank; ``global_batch`` is the batch of ONE data-parallel
     replica. With ``dp_group`` the stage gradients are reduced by the fused NVLink all-reduce as each stage
