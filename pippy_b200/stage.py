@@ -388,7 +388,8 @@ class PipelineStageBase:
         if any(self.output_dests.values()):  # the last stage sends nothing: do not pin its outputs
             self._sent_outputs[mb] = tuple(_detached(o) for o in output_tuple)
         self.fwd_chunk_id = mb + 1
-        logger.debug("[%d] Forwarded chunk %d, outputs: %s", self.stage_index, mb, map_debug_info(output))
+        if logger.isEnabledFor(logging.DEBUG):  # the rendering itself costs more than a small stage's launches
+            logger.debug("[%d] Forwarded chunk %d, outputs: %s", self.stage_index, mb, map_debug_info(output))
         return output
 
     def _parse_chunk_call(self, call_args, call_kwargs, forward: bool):
