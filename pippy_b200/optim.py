@@ -61,19 +61,6 @@ class FlatParams:
                 p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                 p.grad = None
 
-    def buckets(self, bucket_numel: int) -> List[slice]:
-        """Contiguous slices of the flat buffers, cut at parameter boundaries, in reverse parameter order
-        (gradients of late layers are complete first during backward)."""
-        out: List[slice] = []
-        end = self.numel
-        start_idx = len(self.params) - 1
-        cur_end = end
-        for i in range(len(self.params) - 1, -1, -1):
-            if cur_end - self.offsets[i] >= bucket_numel or i == 0:
-                out.append(slice(self.offsets[i], cur_end))
-                cur_end = self.offsets[i]
-        return out
-
 
 class FusedAdamW:
     """AdamW over :class:`FlatParams` buffers. bf16 parameters, fp32 gradients and moments, optional fp32 master
