@@ -76,9 +76,20 @@ def test_looped_bfs_order():
     _check(sched, 2, 2, 3)
 
 
-def test_send_recv_pairing_is_consistent_between_neighbours():
-    P, v, n = 4, 2, 8
-    full = A.add_send_recv(G.zero_bubble(P, v, n), lambda s: s % P, P * v)
+def _deep_costed_order(P, v, n):
+    # the benchmark's case: measured-looking costs with a heavy last stage, up to 8 more microbatches in flight
+    S = P * v
+    cost = {s: (5.5, 6.1, 4.9) for s in range(S)}
+    cost[S - 1] = (6.9, 7.3, 5.8)
+    return G.tuned_zero_bubble_costed(P, v, n, cost, {s: 0.4 for s in range(S - 1)},
+                                      extra_in_flight=(0, 1, 2, 4, 6, 8), pending_w=(P, 2 * P))
+
+
+@pytest.mark.parametrize("P,v,n,make", [(4, 2, 8, G.zero_bubble), (8, 2, 32, _deep_costed_order)])
+def test_send_recv_pairing_is_consistent_between_neighbours(P, v, n, make):
+    order = make(P, v, n)
+    A.validate(order, P * v, n, lambda s: s % P)
+    full = A.add_send_recv(order, lambda s: s % P, P * v)
     # the k-th transfer a rank sends to a peer is the k-th that peer receives from it
     for r in range(P):
         for peer in range(P):
