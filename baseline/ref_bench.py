@@ -9,7 +9,8 @@ Two systems answer to "the reference", and the printed line names which one ran 
   installed torch: PipelineStage + ScheduleInterleaved1F1B, stock code path.  It runs where the reference's own
   interleaved schedule completes no step (four or more ranks; see ``_pippy_blocks``).
 
-Both drive the same ``ref_model.Stage`` slices, the same optimizer and the same watchdog."""
+Both drive the same ``ref_model.Stage`` slices, the same optimizer and the same watchdog.  The composed configs
+(pipeline x data / tensor / expert parallelism) have their arms in ``ref_composed.py``."""
 import json
 import os
 import sys
@@ -101,8 +102,15 @@ def main(args) -> None:
     ref_path = os.path.join(HERE, "_ref")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if getattr(args, "config", "llama7b-pp") != "llama7b-pp":
-        _unavailable(f"the reference arm covers the headline config (llama7b-pp) only; {args.config} composes the "
-                     "pipeline with data, tensor or expert parallelism, which the reference leaves to other libraries")
+        # the composed configs: the pipeline runtime the reference migrated into plus the stock PyTorch library for
+        # the second dimension (DDP, DTensor tensor parallelism, all_to_all_single experts)
+        try:
+            import ref_composed
+
+            ref_composed.run(args, _Watchdog, _unavailable)
+        except Exception as e:
+            traceback.print_exc(file=sys.stderr)
+            _unavailable(f"{type(e).__name__}: {e}")
         return
     system = os.environ.get("PIPPY_REF_SYSTEM") or ("torch.distributed.pipelining" if _pippy_blocks(world) else "pippy")
     if system == "pippy":
