@@ -457,29 +457,61 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ 
   if (warp == 1) tmem_dealloc<1>(tmem_base, 512);
 }
 
-// delta[b, h, s] = sum_d dO * O ; one warp per (token, head)
-__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                float* __restrict__ delta, int B, int S, int Hq, int D, long long do_stride,
-                                long long o_stride) {
-  const long long gw = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long total = (long long)B * S * Hq;
-  if (gw >= total) return;
-  const int h = (int)(gw % Hq);
-  const long long t = gw / Hq;
-  const __nv_bfloat16* a = dO + t * do_stride + h * D;
-  const __nv_bfloat16* c = O + t * o_stride + h * D;
-  float acc = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + i));
-    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(c + i));
-    acc += x.x * y.x + x.y * y.y;
-  }
+// delta[b, h, s] = sum_d dO * O.  D / 8 lanes share one (token, head) row with one 16-byte load each from dO and O;
+// every lane group takes kRows consecutive rows so that 2 * kRows loads are in flight per lane.  Rows are split into
+// (token, head) and tokens into (batch, position) once per thread and then stepped: a division per row made the
+// one-warp-per-row version of this kernel instruction-bound.
+template <int D, int kRows>
+__global__ void __launch_bounds__(256) fa_delta_kernel(const __nv_bfloat16* __restrict__ dO,
+                                                       const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
+                                                       int total, int S, int Hq, long long do_stride,
+                                                       long long o_stride) {
+  constexpr int LPR = D / 8;  // lanes per row: 16 (D = 128) or 8 (D = 64)
+  const int sub = threadIdx.x % LPR;
+  const unsigned group = (blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+  const unsigned first = group * kRows;  // the launcher keeps total + 256 * kRows below 2^31
+  int t = (int)(first / (unsigned)Hq), h = (int)(first - (unsigned)t * Hq);
+  int bb = t / S, s = t - bb * S;
+  const int h0 = h, bb0 = bb, s0 = s;
+  uint4 a[kRows], c[kRows];
+  {
+    long long tt = t;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
-    const long long bb = t / S, s = t % S;
-    delta[(bb * Hq + h) * S + s] = acc;
+    for (int r = 0; r < kRows; ++r) {
+      if (first + r < (unsigned)total) {
+        a[r] = *reinterpret_cast<const uint4*>(dO + tt * do_stride + h * D + sub * 8);
+        c[r] = *reinterpret_cast<const uint4*>(O + tt * o_stride + h * D + sub * 8);
+      } else {
+        a[r] = make_uint4(0, 0, 0, 0);
+        c[r] = make_uint4(0, 0, 0, 0);
+      }
+      if (++h == Hq) {
+        h = 0;
+        ++tt;
+      }
+    }
+  }
+  h = h0, bb = bb0, s = s0;
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a[r]);
+    const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&c[r]);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 xf = __bfloat1622float2(x[i]), yf = __bfloat1622float2(y[i]);
+      acc += xf.x * yf.x + xf.y * yf.y;
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (sub == 0 && first + r < (unsigned)total) delta[((long long)bb * Hq + h) * S + s] = acc;
+    if (++h == Hq) {
+      h = 0;
+      if (++s == S) {
+        s = 0;
+        ++bb;
+      }
+    }
   }
 }
 
@@ -516,15 +548,22 @@ int pb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, co
   if (Hq % Hkv != 0) return -2;
   if ((q_stride % 8) || (k_stride % 8) || (v_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dqkv_stride % 8))
     return -3;
+  if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(o)) & 15) return -3;  // 16-byte loads below
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const uint64_t T = (uint64_t)B * S;
   {
-    const long long warps = (long long)T * Hq;
-    const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
-    fa_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dO),
-                                                              reinterpret_cast<const __nv_bfloat16*>(o), delta, B, S,
-                                                              Hq, D, do_stride, o_stride);
+    constexpr int kRows = 4;
+    const long long rows = (long long)T * Hq;
+    if (rows > 0x7fffffffLL - 256 * kRows) return -4;  // the delta kernel indexes rows with 32 bits
+    const int lpr = D / 8;
+    const long long threads_needed = (rows + kRows - 1) / kRows * lpr;
+    const unsigned blocks = (unsigned)((threads_needed + 255) / 256);
+    auto DO = reinterpret_cast<const __nv_bfloat16*>(dO);
+    auto OO = reinterpret_cast<const __nv_bfloat16*>(o);
+    if (D == 128)
+      fa_delta_kernel<128, kRows><<<blocks, 256, 0, stream>>>(DO, OO, delta, (int)rows, S, Hq, do_stride, o_stride);
+    else
+      fa_delta_kernel<64, kRows><<<blocks, 256, 0, stream>>>(DO, OO, delta, (int)rows, S, Hq, do_stride, o_stride);
     pb_count_launch(1);
   }
   CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64;

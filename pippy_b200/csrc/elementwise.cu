@@ -67,40 +67,53 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf
 // gu: [T, 2F] (gate | up) -> out [T, F] = silu(gate) * up
 // row_limit (optional, device): only rows below *row_limit are processed (buffers sized for a capacity of which the
 // device knows how much is in use)
-__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
-                                  int F, const int* __restrict__ row_limit) {
-  const int vec = F / 8;
+// Thread layout of both SwiGLU kernels: x covers the 16-byte column vectors of a row, y strides over the rows, so
+// that no index is ever divided (a flat index split by 64-bit division made these kernels instruction-bound).
+__global__ void __launch_bounds__(128) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
+                                                         __nv_bfloat16* __restrict__ out, long long T, int F,
+                                                         const int* __restrict__ row_limit) {
   if (row_limit && *row_limit < T) T = *row_limit;
-  const long long total = T * vec;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / vec;
-    const int v = (int)(i % vec);
-    const __nv_bfloat16* row = gu + t * 2 * F;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= F / 8) return;
+  const long long step = gridDim.y;
+  // two rows per trip: four 16-byte loads in flight per thread
+  for (long long t = blockIdx.y; t < T; t += 2 * step) {
+    const long long t1 = t + step < T ? t + step : t;
+    const __nv_bfloat16* r0 = gu + t * 2 * F + v * 8;
+    const __nv_bfloat16* r1 = gu + t1 * 2 * F + v * 8;
+    const uint4 g0 = *reinterpret_cast<const uint4*>(r0);
+    const uint4 u0 = *reinterpret_cast<const uint4*>(r0 + F);
+    const uint4 g1 = *reinterpret_cast<const uint4*>(r1);
+    const uint4 u1 = *reinterpret_cast<const uint4*>(r1 + F);
     float g[8], u[8], o[8];
-    unpack8(*reinterpret_cast<const uint4*>(row + v * 8), g);
-    unpack8(*reinterpret_cast<const uint4*>(row + F + v * 8), u);
+    unpack8(g0, g);
+    unpack8(u0, u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j];
     *reinterpret_cast<uint4*>(out + t * F + v * 8) = pack8(o);
+    if (t1 != t) {
+      unpack8(g1, g);
+      unpack8(u1, u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j];
+      *reinterpret_cast<uint4*>(out + t1 * F + v * 8) = pack8(o);
+    }
   }
 }
 
 // dgu [T, 2F] from dout [T, F] and gu
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ dgu, long long T, int F,
-                                  const int* __restrict__ row_limit) {
-  const int vec = F / 8;
+__global__ void __launch_bounds__(128) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                                         const __nv_bfloat16* __restrict__ gu,
+                                                         __nv_bfloat16* __restrict__ dgu, long long T, int F,
+                                                         const int* __restrict__ row_limit) {
   if (row_limit && *row_limit < T) T = *row_limit;
-  const long long total = T * vec;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / vec;
-    const int v = (int)(i % vec);
-    const __nv_bfloat16* row = gu + t * 2 * F;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= F / 8) return;
+  for (long long t = blockIdx.y; t < T; t += gridDim.y) {
+    const __nv_bfloat16* row = gu + t * 2 * F + v * 8;
     float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(*reinterpret_cast<const uint4*>(row + v * 8), g);
-    unpack8(*reinterpret_cast<const uint4*>(row + F + v * 8), u);
+    unpack8(*reinterpret_cast<const uint4*>(row), g);
+    unpack8(*reinterpret_cast<const uint4*>(row + F), u);
     unpack8(*reinterpret_cast<const uint4*>(dout + t * F + v * 8), d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -222,6 +235,15 @@ static inline int grid_for(long long work_items, int threads) {
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
+// x: 128-thread CTAs over the F / 8 column vectors; y: rows, about 32 CTAs per SM in all
+static inline dim3 swiglu_grid(long long T, int F) {
+  const int gx = (F / 8 + 127) / 128;
+  long long gy = (148LL * 32 + gx - 1) / gx;
+  if (gy > T) gy = T;
+  if (gy < 1) gy = 1;
+  return dim3((unsigned)gx, (unsigned)gy);
+}
+
 }  // namespace pbe
 
 extern "C" {
@@ -242,9 +264,8 @@ int pb_swiglu_fwd(const void* gu, void* out, long long T, int F, const int* row_
   using namespace pbe;
   if (F % 8 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
-                                                                     reinterpret_cast<__nv_bfloat16*>(out), T, F,
-                                                                     row_limit);
+  swiglu_fwd_kernel<<<swiglu_grid(T, F), 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
+                                                           reinterpret_cast<__nv_bfloat16*>(out), T, F, row_limit);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }
@@ -254,9 +275,9 @@ int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int 
   using namespace pbe;
   if (F % 8 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dout), reinterpret_cast<const __nv_bfloat16*>(gu),
-      reinterpret_cast<__nv_bfloat16*>(dgu), T, F, row_limit);
+  swiglu_bwd_kernel<<<swiglu_grid(T, F), 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                           reinterpret_cast<const __nv_bfloat16*>(gu),
+                                                           reinterpret_cast<__nv_bfloat16*>(dgu), T, F, row_limit);
   pb_count_launch(1);
   return (int)cudaGetLastError();
 }

@@ -7,6 +7,7 @@
     python -m pippy_b200.ops.bench_kernels grouped            # grouped expert GEMMs vs a loop of plain GEMMs / cuBLAS
     python -m pippy_b200.ops.bench_kernels grouped-once       # three grouped launches on a small case, for ncu
     python -m pippy_b200.ops.bench_kernels route              # MoE router kernels vs the eager statement
+    python -m pippy_b200.ops.bench_kernels elementwise        # RMSNorm, SwiGLU, attention delta on one 7B microbatch
     python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe | peer-copy
 
 Library rates (cuBLAS via torch.matmul, SDPA) are printed beside ours for scale.
@@ -426,6 +427,70 @@ def grouped_once():
     print("grouped-once done", float(y[:2300].float().abs().mean()))
 
 
+def bench_elementwise():
+    """Memory-bound kernels on one Llama-2-7B microbatch (T 8192, d 4096, ffn 11008), called through the C entry
+    points so that no autograd bookkeeping sits between launches.  Each launch works on the next of three buffer sets
+    (together larger than L2); the rate is algorithmic bytes over the CUDA-event time."""
+    from . import _lib
+    from .functional import _ensure_restypes, _norm_scratch, sm_count
+
+    _ensure_restypes()
+    L = _lib.lib()
+    T, H, F = 8192, 4096, 11008
+    dev = torch.device("cuda")
+    sets = 3
+    x = [torch.randn(T, H, device=dev).bfloat16() for _ in range(sets)]
+    dy = [torch.randn(T, H, device=dev).bfloat16() for _ in range(sets)]
+    y = [torch.empty(T, H, device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+    w = torch.randn(H, device=dev).bfloat16()
+    rstd = torch.empty(T, device=dev, dtype=torch.float32)
+    dw = torch.zeros(H, device=dev, dtype=torch.float32)
+    scratch = _norm_scratch(H, dev)
+    gu = [torch.randn(T, 2 * F, device=dev).bfloat16() for _ in range(sets)]
+    h = [torch.empty(T, F, device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+    dgu = [torch.empty(T, 2 * F, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    k = [0]
+
+    def nxt():
+        k[0] = (k[0] + 1) % sets
+        return k[0]
+
+    def norm_fwd():
+        i = nxt()
+        _lib.check(L.pb_norm_fwd(_lib.ptr(x[i]), _lib.ptr(w), _lib.ptr(None), _lib.ptr(y[i]), _lib.ptr(None),
+                                 _lib.ptr(rstd), _lib.c_int(T), _lib.c_int(H), _lib.c_float(1e-5), _lib.c_int(0),
+                                 _lib.stream_ptr()), "pb_norm_fwd")
+
+    def norm_bwd():
+        i = nxt()
+        _lib.check(L.pb_norm_bwd(_lib.ptr(dy[i]), _lib.ptr(x[i]), _lib.ptr(w), _lib.ptr(None), _lib.ptr(rstd),
+                                 _lib.ptr(y[i]), _lib.ptr(dw), _lib.ptr(None), _lib.ptr(None), _lib.ptr(None),
+                                 _lib.c_int(1), _lib.ptr(scratch), _lib.c_int(T), _lib.c_int(H), _lib.c_int(0),
+                                 _lib.c_int(sm_count()), _lib.stream_ptr()), "pb_norm_bwd")
+
+    def swiglu_fwd():
+        i = nxt()
+        _lib.check(L.pb_swiglu_fwd(_lib.ptr(gu[i]), _lib.ptr(h[i]), _lib.c_ll(T), _lib.c_int(F), _lib.ptr(None),
+                                   _lib.stream_ptr()), "pb_swiglu_fwd")
+
+    def swiglu_bwd():
+        i = nxt()
+        _lib.check(L.pb_swiglu_bwd(_lib.ptr(h[i]), _lib.ptr(gu[i]), _lib.ptr(dgu[i % 2]), _lib.c_ll(T), _lib.c_int(F),
+                                   _lib.ptr(None), _lib.stream_ptr()), "pb_swiglu_bwd")
+
+    cases = [
+        ("norm_fwd (RMSNorm)", norm_fwd, 2 * T * H * 2),
+        ("norm_bwd + partial fold", norm_bwd, 3 * T * H * 2),
+        ("swiglu_fwd", swiglu_fwd, 3 * T * F * 2),
+        ("swiglu_bwd", swiglu_bwd, 5 * T * F * 2),
+    ]
+    norm_fwd()  # rstd of a real input for the backward
+    for name, fn, nbytes in cases:
+        ms = _time(fn, iters=30)
+        print(f"{name:26s} {ms * 1e3:7.1f} us  {nbytes / ms / 1e9:6.2f} TB/s")
+    _lib.check_device_errors()
+
+
 def bench_route():
     """Router kernels (softmax, top-2, weights, aux loss, positions: two launches) against the eager statement."""
     from ..parallel.ep import EPContext, _Plan, _RouteFn
@@ -452,7 +517,7 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "gemm-once": gemm_once, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
      "dp": bench_dp, "moe": bench_moe, "peer-copy": bench_peer_copy, "grouped": bench_grouped, "grouped-once": grouped_once,
-     "route": bench_route}[what]()
+     "route": bench_route, "elementwise": bench_elementwise}[what]()
     from . import _lib
 
     _lib.check_device_errors()
