@@ -713,6 +713,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// Tile order knob: output tiles are walked in bands of `group_m` row tiles, row-fastest inside a band (0 = default).
+static int g_group_m = 0;
+
 template <int kCtaGroup, int BN, int kStages>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sm_count,
                        cudaStream_t stream, const CUtensorMap* tmA2 = nullptr, int copy_ctas = 0,
@@ -732,6 +735,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.num_n_tiles = (p.N + BN - 1) / BN;
   p.num_k_blocks = (p.K + BK - 1) / BK;
   p.group_m = kCtaGroup == 1 ? 16 : 8;
+  if (g_group_m > 0 && !p.fused) p.group_m = g_group_m;
   // grouped M: up to one partial tile per group on top of the dense count (p.M is the buffers' row capacity)
   const int tiles = (p.num_m_tiles + (p.grouped == 1 ? p.n_groups : 0)) * p.num_n_tiles * tile_multiplier;
   int units = (sm_count - copy_ctas) / kCtaGroup;
@@ -770,6 +774,9 @@ extern "C" {
 // Leaves `n` SMs out of the persistent GEMM grid (for communication kernels that must run beside it).
 void pb_set_sm_reserve(int n) { g_sm_reserve = n < 0 ? 0 : n; }
 int pb_get_sm_reserve() { return g_sm_reserve; }
+
+// Rows of output tiles per band of the tile order of the plain and grouped GEMMs (0 restores the default).
+void pb_set_gemm_group_m(int n) { pb::g_group_m = n < 0 ? 0 : n; }
 
 // C[M,N] = A.B^T with fused epilogue.  A: a_mn ? [K, M] (ld = lda) : [M, K];  B: b_mn ? [K, N] : [N, K].
 // variant: 0 = automatic, 1 = single-CTA tiles (128 x 256), 2 = CTA-pair tiles (256 x 256),
