@@ -8,6 +8,7 @@
     python -m pippy_b200.ops.bench_kernels grouped-once       # three grouped launches on a small case, for ncu
     python -m pippy_b200.ops.bench_kernels route              # MoE router kernels vs the eager statement
     python -m pippy_b200.ops.bench_kernels elementwise        # RMSNorm, SwiGLU, attention delta on one 7B microbatch
+    python -m pippy_b200.ops.bench_kernels elementwise-once   # one launch of each of them, for ncu
     python -m torch.distributed.run --nproc-per-node 2 -m pippy_b200.ops.bench_kernels tp | dp | moe | peer-copy
 
 Library rates (cuBLAS via torch.matmul, SDPA) are printed beside ours for scale.
@@ -427,7 +428,7 @@ def grouped_once():
     print("grouped-once done", float(y[:2300].float().abs().mean()))
 
 
-def bench_elementwise():
+def bench_elementwise(once: bool = False):
     """Memory-bound kernels on one Llama-2-7B microbatch (T 8192, d 4096, ffn 11008), called through the C entry
     points so that no autograd bookkeeping sits between launches.  Each launch works on the next of three buffer sets
     (together larger than L2); the rate is algorithmic bytes over the CUDA-event time."""
@@ -438,7 +439,7 @@ def bench_elementwise():
     L = _lib.lib()
     T, H, F = 8192, 4096, 11008
     dev = torch.device("cuda")
-    sets = 3
+    sets = 1 if once else 3
     x = [torch.randn(T, H, device=dev).bfloat16() for _ in range(sets)]
     dy = [torch.randn(T, H, device=dev).bfloat16() for _ in range(sets)]
     y = [torch.empty(T, H, device=dev, dtype=torch.bfloat16) for _ in range(sets)]
@@ -485,6 +486,12 @@ def bench_elementwise():
         ("swiglu_bwd", swiglu_bwd, 5 * T * F * 2),
     ]
     norm_fwd()  # rstd of a real input for the backward
+    if once:
+        for _, fn, _ in cases:
+            fn()
+        torch.cuda.synchronize()
+        _lib.check_device_errors()
+        return
     for name, fn, nbytes in cases:
         ms = _time(fn, iters=30)
         print(f"{name:26s} {ms * 1e3:7.1f} us  {nbytes / ms / 1e9:6.2f} TB/s")
@@ -517,7 +524,8 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "gemm-once": gemm_once, "attention": bench_attention, "attention-once": attention_once, "tp": bench_tp,
      "dp": bench_dp, "moe": bench_moe, "peer-copy": bench_peer_copy, "grouped": bench_grouped, "grouped-once": grouped_once,
-     "route": bench_route, "elementwise": bench_elementwise}[what]()
+     "route": bench_route, "elementwise": bench_elementwise,
+     "elementwise-once": lambda: bench_elementwise(once=True)}[what]()
     from . import _lib
 
     _lib.check_device_errors()
