@@ -287,6 +287,8 @@ def build_job(args, world, rank, device, dtype):
     if args.config == "gpt2-pp4dp2":
         vocab, n_pos, d, n_layers, heads = 50257, 1024, 768, 12, 12
         n_layers = getattr(args, "layers", None) or n_layers
+        if os.environ.get("PIPPY_REF_TINY"):
+            vocab, d, heads = 512, 128, 2
         mod = GPT2Stage(_even_layers(n_layers, pp_rank, pp), first, last, vocab, max(n_pos, seq), d, heads, dtype, device)
         module = DDP(mod, process_group=in_group, **ddp_kw) if inner > 1 else mod
         replicas, replica = inner, in_rank

@@ -122,12 +122,15 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const __nv_bfloat16* 
 }
 
 // dx and per-CTA partial dw (and db). partial: [gridDim.x, 2, H] fp32 (db half unused for RMSNorm).
-template <bool kLayer, int NV>
+// dres (optional, [T, H]): a gradient that reached x on another path (the residual branch); it is added to dx here
+// instead of by a separate elementwise kernel.
+template <bool kLayer, int NV, bool kRes>
 __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                            const __nv_bfloat16* __restrict__ x,
                                                            const __nv_bfloat16* __restrict__ w,
                                                            const float* __restrict__ mean_in,
                                                            const float* __restrict__ rstd_in,
+                                                           const __nv_bfloat16* __restrict__ dres,
                                                            __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
                                                            int T, int H) {
   __shared__ float red[THREADS / 32];
@@ -146,17 +149,19 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* 
   }
   // The next row's loads are issued before this row's reductions: the block-wide sums wait at barriers, and
   // without loads in flight across them the kernel ran at half of the copy bandwidth.
-  uint4 xq[NV], gq[NV];
+  uint4 xq[NV], gq[NV], rq[NV];
   float rstd_next = 0.f, mean_next = 0.f;
   auto fetch = [&](int row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    const uint4* rr = kRes ? reinterpret_cast<const uint4*>(dres + (size_t)row * H) : nullptr;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = threadIdx.x + i * THREADS;
       if (c < nvec) {
         xq[i] = xr[c];
         gq[i] = gr[c];
+        if (kRes) rq[i] = rr[c];
       }
     }
     rstd_next = rstd_in[row];
@@ -167,6 +172,7 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* 
     const float rstd = rstd_next;
     const float mean = kLayer ? mean_next : 0.f;
     float xh[NV][8], g[NV][8];
+    uint4 rcur[NV];
     float s1 = 0.f, s2 = 0.f;  // sum(g*w*xhat), sum(g*w)
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -174,6 +180,7 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* 
       if (c < nvec) {
         unpack8(xq[i], xh[i]);
         unpack8(gq[i], g[i]);
+        if (kRes) rcur[i] = rq[i];
       }
     }
     if (row + (int)gridDim.x < T) fetch(row + gridDim.x);
@@ -202,6 +209,12 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const __nv_bfloat16* 
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] * wv[i][j] - m2 - xh[i][j] * m1);
+        if (kRes) {
+          float r[8];
+          unpack8(rcur[i], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
         dxr[c] = pack8(o);
       }
     }
@@ -287,9 +300,10 @@ int pb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mea
 }
 
 // dw_f32/db_f32 (fp32, accumulate) or dw_bf16/db_bf16; scratch: pb_norm_bwd_scratch_floats(H, sm_count) floats.
-int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
-                float* dw_f32, float* db_f32, void* dw_bf16, void* db_bf16, int accumulate, float* scratch, int T, int H,
-                int layer_norm, int sm_count, void* stream_) {
+// dres: optional [T, H] bf16 gradient added to dx (the residual branch's gradient of the same tensor).
+int pb_norm_bwd_res(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                    const void* dres, void* dx, float* dw_f32, float* db_f32, void* dw_bf16, void* db_bf16,
+                    int accumulate, float* scratch, int T, int H, int layer_norm, int sm_count, void* stream_) {
   using namespace pbn;
   if (H % 8 != 0 || H > THREADS * MAX_VEC * 8) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -300,7 +314,12 @@ int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
   const int nv = (H / 8 + THREADS - 1) / THREADS;
-#define PB_BWD(L, NVV) norm_bwd_kernel<L, NVV><<<grid, THREADS, 0, stream>>>(DY, X, W, mean, rstd, DX, scratch, T, H)
+  auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
+#define PB_BWD(L, NVV)                                                                                          \
+  do {                                                                                                          \
+    if (DR) norm_bwd_kernel<L, NVV, true><<<grid, THREADS, 0, stream>>>(DY, X, W, mean, rstd, DR, DX, scratch, T, H); \
+    else norm_bwd_kernel<L, NVV, false><<<grid, THREADS, 0, stream>>>(DY, X, W, mean, rstd, DR, DX, scratch, T, H);   \
+  } while (0)
   if (layer_norm) {
     if (nv <= 1) PB_BWD(true, 1); else if (nv <= 2) PB_BWD(true, 2); else PB_BWD(true, 4);
   } else {
@@ -318,6 +337,13 @@ int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
   }
   pb_count_launch(launches);
   return (int)cudaGetLastError();
+}
+
+int pb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                float* dw_f32, float* db_f32, void* dw_bf16, void* db_bf16, int accumulate, float* scratch, int T, int H,
+                int layer_norm, int sm_count, void* stream_) {
+  return pb_norm_bwd_res(dy, x, w, mean, rstd, nullptr, dx, dw_f32, db_f32, dw_bf16, db_bf16, accumulate, scratch, T, H,
+                         layer_norm, sm_count, stream_);
 }
 
 }  // extern "C"
@@ -370,9 +396,9 @@ int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const f
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
   const int nv = (H / 8 + THREADS - 1) / THREADS;
   // every CTA overwrites its own partial row before the fold reads it, so nothing needs clearing between calls
-  if (nv <= 1) norm_bwd_kernel<false, 1><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
-  else if (nv <= 2) norm_bwd_kernel<false, 2><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
-  else norm_bwd_kernel<false, 4><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, DX, scratch, T, H);
+  if (nv <= 1) norm_bwd_kernel<false, 1, false><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, nullptr, DX, scratch, T, H);
+  else if (nv <= 2) norm_bwd_kernel<false, 2, false><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, nullptr, DX, scratch, T, H);
+  else norm_bwd_kernel<false, 4, false><<<grid, THREADS, 0, stream>>>(DY, X, W, nullptr, rstd, nullptr, DX, scratch, T, H);
   norm_reduce_partials<<<(H + RED_COLS - 1) / RED_COLS, RED_COLS * RED_WAYS, 0, stream>>>(scratch, grid, H, 0, dw_f32,
                                                                                           nullptr, accumulate);
   pb_count_launch(2);

@@ -44,6 +44,10 @@ class RMSNorm(nn.Module):
     def forward(self, x):
         return pf.rms_norm(x, self.weight, self.eps)
 
+    def fork(self, x):
+        """``(norm(x), x)``; pass the second result to the residual add (see ``pf.rms_norm_fork``)."""
+        return pf.rms_norm_fork(x, self.weight, self.eps)
+
 
 class LayerNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5, device=None, dtype=None):

@@ -145,12 +145,16 @@ class LlamaBlock(nn.Module):
         by the previous stage when this block starts at a2 or f2.  Returns ``x`` (or ``(x, carry)`` when the block
         ends at a1 or f1)."""
         u = self.units
+        # norm.fork: the residual operand is the norm's second result, so that the residual branch's gradient is
+        # added inside the norm-backward kernel
         if "a1" in u:
-            carry = self.attention.core(self.attention_norm(x), B, S)
+            n, x = self.attention_norm.fork(x)
+            carry = self.attention.core(n, B, S)
         if "a2" in u:
             x, carry = self.attention.wo(carry, residual=x), None
         if "f1" in u:
-            carry = pf.swiglu(self.feed_forward.w_gate_up(self.ffn_norm(x)))
+            n, x = self.ffn_norm.fork(x)
+            carry = pf.swiglu(self.feed_forward.w_gate_up(n))
         if "f2" in u:
             x, carry = self.feed_forward.w_down(carry, residual=x), None
         return x if carry is None else (x, carry)

@@ -194,8 +194,12 @@ def _ensure_restypes():
 
 
 class _NormFn(torch.autograd.Function):
+    """``fork=True`` also returns the input itself as a second output: the caller feeds THAT to the residual
+    branch, so both gradients of the tensor arrive here and the backward kernel adds the residual one to dx
+    (autograd would otherwise sum them with an elementwise kernel of its own)."""
+
     @staticmethod
-    def forward(ctx, x, weight, bias, eps: float, layer: bool):
+    def forward(ctx, x, weight, bias, eps: float, layer: bool, fork: bool):
         _ensure_restypes()
         H = x.shape[-1]
         x2 = x.reshape(-1, H)
@@ -219,16 +223,27 @@ class _NormFn(torch.autograd.Function):
         ctx.bias = bias
         ctx.layer = layer
         ctx.x_shape = x.shape
+        ctx.set_materialize_grads(False)  # an unused branch of the fork arrives as None, not as a tensor of zeros
+        if fork:
+            return y.view(x.shape), x
         return y.view(x.shape)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x2, mean, rstd = ctx.saved_tensors
         weight, bias = ctx.weight, ctx.bias
         T, H = x2.shape
+        if dy is None:  # only the residual branch was used
+            return dres, None, None, None, None, None
         dy2 = dy.reshape(T, H)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        if dres is not None:
+            dres = dres.reshape(T, H)
+            if dres.dtype != x2.dtype:
+                dres = dres.to(x2.dtype)
+            if not dres.is_contiguous():
+                dres = dres.contiguous()
         dx = torch.empty_like(x2)
         wmg = getattr(weight, "main_grad", None)
         use_main = wmg is not None and wmg.dtype == torch.float32
@@ -238,23 +253,32 @@ class _NormFn(torch.autograd.Function):
             bmg = getattr(bias, "main_grad", None)
             db = bmg if (use_main and bmg is not None) else torch.empty(H, dtype=torch.float32, device=x2.device)
         _lib.check(
-            _lib.lib().pb_norm_bwd(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(weight), _lib.ptr(mean), _lib.ptr(rstd),
-                                   _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(db), _lib.ptr(None), _lib.ptr(None),
-                                   _lib.c_int(int(use_main)), _lib.ptr(_norm_scratch(H, x2.device)), _lib.c_int(T),
-                                   _lib.c_int(H), _lib.c_int(int(ctx.layer)), _lib.c_int(sm_count()),
-                                   _lib.stream_ptr()),
-            "pb_norm_bwd",
+            _lib.lib().pb_norm_bwd_res(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(weight), _lib.ptr(mean), _lib.ptr(rstd),
+                                       _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(db), _lib.ptr(None),
+                                       _lib.ptr(None), _lib.c_int(int(use_main)),
+                                       _lib.ptr(_norm_scratch(H, x2.device)), _lib.c_int(T), _lib.c_int(H),
+                                       _lib.c_int(int(ctx.layer)), _lib.c_int(sm_count()), _lib.stream_ptr()),
+            "pb_norm_bwd_res",
         )
         if not use_main:
             _accumulate_param_grad(weight, dw)
             if ctx.layer:
                 _accumulate_param_grad(bias, db)
-        return dx.view(ctx.x_shape), None, None, None, None
+        return dx.view(ctx.x_shape), None, None, None, None, None
+
+
+def rms_norm_fork(x, weight, eps: float = 1e-5):
+    """``(rms_norm(x), x)`` for the pre-norm residual pattern ``x + f(norm(x))``: use the second result as the
+    residual operand.  On the kernel path the gradient that comes back through it is added to the norm's input
+    gradient inside the norm-backward kernel."""
+    if _use_kernels(x):
+        return _NormFn.apply(x, weight, None, eps, False, True)
+    return rms_norm(x, weight, eps), x
 
 
 def rms_norm(x, weight, eps: float = 1e-5):
     if _use_kernels(x):
-        return _NormFn.apply(x, weight, None, eps, False)
+        return _NormFn.apply(x, weight, None, eps, False, False)
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     return (y * weight.float()).to(x.dtype)
@@ -262,7 +286,7 @@ def rms_norm(x, weight, eps: float = 1e-5):
 
 def layer_norm(x, weight, bias, eps: float = 1e-5):
     if _use_kernels(x):
-        return _NormFn.apply(x, weight, bias, eps, True)
+        return _NormFn.apply(x, weight, bias, eps, True, False)
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 

@@ -350,3 +350,56 @@ def _llama_tp_pp(rank, world):
 
 def test_llama_tp2_pp2_matches_unsharded_model():
     run_ranks(_llama_tp_pp, 4, timeout_s=240)
+
+
+def _unit_cut_partitions_match_single_stage(dev):
+    """A two-layer Llama cut after EVERY unit of a layer (eight stages on one rank: boundaries after a1 and f1 hand
+    over the residual stream together with the attention / SwiGLU output, and the residual stream leaves such a
+    stage as the fork of its norm) gives the loss and the gradients of the single-stage model, weight for weight."""
+    from pippy_b200.models.llama import LlamaConfig
+    from pippy_b200.train import build_llama_pipeline
+
+    cfg = LlamaConfig(vocab_size=1024, dim=512, n_layers=2, n_heads=4, ffn_dim=1024)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (4, 256), device=dev)
+    res, weights = {}, None
+    for v, sched in ((1, "1f1b"), (8, "interleaved_1f1b"), (8, "zero_bubble")):
+        pipe = build_llama_pipeline(cfg, 4, 256, 2, dev, schedule=sched, virtual_stages=v, seed=11, with_optimizer=True)
+        pipe.optimizer = None  # keep the accumulated gradients
+        if weights is None:
+            weights = {n: p.detach().clone() for st in pipe.stages for n, p in st.submod.named_parameters()}
+        else:
+            units = [b.units for st in pipe.stages for b in st.submod.layers.values()]
+            assert ("a1",) in units and ("f1",) in units, units
+            with torch.no_grad():
+                for st in pipe.stages:
+                    for n, p in st.submod.named_parameters():
+                        p.copy_(weights[n])
+        loss = float(pipe.train_step(ids, ids))
+        grads = {}
+        for st in pipe.stages:
+            for n, p in st.submod.named_parameters():
+                grads[n] = (p.main_grad if p.grad is None else p.grad).float().clone()
+        res[(v, sched)] = (loss, grads)
+    base_loss, base = res[(1, "1f1b")]
+    assert all(g.abs().max().item() > 0 for g in base.values())
+    for key in ((8, "interleaved_1f1b"), (8, "zero_bubble")):
+        loss, g = res[key]
+        assert sorted(g) == sorted(base)
+        assert abs(loss - base_loss) < 1e-6, key
+        for n in base:
+            rel = ((g[n] - base[n]).abs().max() / base[n].abs().max().clamp(min=1e-9)).item()
+            assert rel < 1e-3, (key, n, rel)
+
+
+def test_unit_cut_partitions_match_single_stage():
+    _unit_cut_partitions_match_single_stage(torch.device("cpu"))
+
+
+@pytest.mark.gpu
+def test_unit_cut_partitions_match_single_stage_on_the_kernels():
+    from pippy_b200.ops import _lib
+
+    _unit_cut_partitions_match_single_stage(torch.device("cuda", 0))
+    torch.cuda.synchronize()
+    _lib.check_device_errors()

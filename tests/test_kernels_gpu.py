@@ -82,6 +82,64 @@ def test_norm(H, layer):
         assert _rel(b.grad, bf.grad) < 2e-2
 
 
+def test_norm_fork_adds_the_residual_gradient():
+    """``rms_norm_fork`` hands back its input for the residual branch; the gradient that returns through it is added
+    to the norm's input gradient by the backward kernel."""
+    from pippy_b200.ops import functional as pf
+
+    T, H = 515, 4096
+    x = _bf16(T, H).requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_()
+    dy, dr = _bf16(T, H), _bf16(T, H)
+    y, xr = pf.rms_norm_fork(x, w, 1e-5)
+    assert xr.data_ptr() == x.data_ptr()
+    torch.autograd.backward([y, xr], [dy, dr])
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    torch.autograd.backward([yr, xf * 1.0], [dy.float(), dr.float()])
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xf.grad) < 1e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
+    # only the residual branch used: the gradient passes through
+    x2 = _bf16(T, H).requires_grad_()
+    _, xr2 = pf.rms_norm_fork(x2, w, 1e-5)
+    xr2.backward(dr)
+    assert torch.equal(x2.grad, dr)
+
+
+def test_llama_block_matches_fp32_reference():
+    """One decoder layer on the kernels (bf16) against the same layer's plain PyTorch path in fp32 on the CPU:
+    output, input gradient and the gradients of both norm weights and of the down projection."""
+    from pippy_b200.models.llama import LlamaBlock, LlamaConfig
+
+    cfg = LlamaConfig(vocab_size=256, dim=512, n_layers=1, n_heads=4, ffn_dim=1024)
+    B, S = 2, 128
+    torch.manual_seed(3)
+    ref = LlamaBlock(cfg, dtype=torch.float32)
+    with torch.no_grad():
+        for name, prm in ref.named_parameters():
+            if name.endswith("norm.weight"):
+                prm.add_(0.1 * torch.randn_like(prm))
+            prm.copy_(prm.bfloat16().float())  # both sides start from the same bf16-representable weights
+    blk = LlamaBlock(cfg, device="cuda", dtype=torch.bfloat16)
+    blk.load_state_dict({k: v.bfloat16() for k, v in ref.state_dict().items()})
+    x = (0.5 * torch.randn(B * S, cfg.dim)).bfloat16()
+    dy = (0.1 * torch.randn(B * S, cfg.dim)).bfloat16()
+    xg = x.cuda().requires_grad_()
+    out = blk(xg, B, S)
+    out.backward(dy.cuda())
+    xr = x.float().requires_grad_()
+    out_ref = ref(xr, B, S)
+    out_ref.backward(dy.float())
+    assert _rel(out.cpu(), out_ref) < 2e-2
+    assert _rel(xg.grad.cpu(), xr.grad) < 3e-2
+    got = dict(blk.named_parameters())
+    for name in ("attention_norm.weight", "ffn_norm.weight", "feed_forward.w_down.weight"):
+        want = dict(ref.named_parameters())[name].grad
+        g = got[name].grad if got[name].grad is not None else got[name].main_grad
+        assert _rel(g.cpu(), want) < 5e-2, name
+
+
 def test_swiglu_and_gelu_linear():
     from pippy_b200.ops import functional as pf
 

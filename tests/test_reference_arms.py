@@ -19,7 +19,7 @@ def _free_port() -> int:
 
 
 @pytest.mark.parametrize("config,inner,parallelism,vocab", [
-    ("gpt2-pp4dp2", 2, "pp2xdp2", 50257),
+    ("gpt2-pp4dp2", 2, "pp2xdp2", 512),
     ("llama13b-tp4pp2", 2, "tp2xpp2", 512),
     ("mixtral-pp2ep4", 2, "pp2xep2", 512),
 ])
